@@ -1,0 +1,99 @@
+// Host-side helpers shared by the launchers: error codes, TMA tensor-map encoding through the
+// driver entry point (no link-time dependency on libcuda), device properties.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace dptb {
+
+// Return codes of every extern "C" entry point: 0 = ok, > 0 = cudaError_t, < 0 = library error.
+enum HostError : int {
+  kErrBadShape = -1,      // shape / stride / alignment the kernel cannot take
+  kErrNoDriver = -2,      // cuTensorMapEncodeTiled could not be resolved
+  kErrTensorMap = -3,     // the driver rejected a tensor map
+  kErrTooLarge = -4,      // a fixed-capacity scratch area is too small for this call
+  kErrUnsupported = -5,
+};
+
+#define DPTB_CUDA_OK(expr)                     \
+  do {                                         \
+    cudaError_t _e = (expr);                   \
+    if (_e != cudaSuccess) return (int)_e;     \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map with 128-byte swizzle.  `inner` is the contiguous extent (elements), `outer` the number of rows,
+// `row_stride_bytes` the distance between rows (multiple of 16).  Out-of-range reads give zeros.
+inline int encode_tmap_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                               uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_tiled();
+  if (!fn) return kErrNoDriver;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) || box_inner * 2 > 128 || box_outer > 256)
+    return kErrBadShape;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+// 4-D bf16 tensor map with 128-byte swizzle: dims[0] is contiguous; strides[i] (bytes) is the stride of dims[i+1].
+inline int encode_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims_in[4],
+                               const uint64_t strides_bytes[3], const uint32_t box_in[4]) {
+  EncodeTiledFn fn = get_encode_tiled();
+  if (!fn) return kErrNoDriver;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return kErrBadShape;
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 4; ++i) {
+    dims[i] = dims_in[i];
+    box[i] = box_in[i];
+  }
+  for (int i = 0; i < 3; ++i) {
+    if (strides_bytes[i] & 15) return kErrBadShape;
+    strides[i] = strides_bytes[i];
+  }
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
+}
+
+inline int sm_count() {
+  static int cached[16] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace dptb

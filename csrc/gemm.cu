@@ -1,0 +1,533 @@
+// bf16 GEMM on 5th-generation tensor cores (tcgen05 + TMEM) with fused epilogues, plus a plain
+// SIMT kernel for shapes / dtypes the tensor-core path cannot take.
+//
+//   C[M,N] = epilogue( op(A)[M,K] * op(B)[K,N] )
+//
+// It replaces the reference's single 32x32 shared-memory-tiled fp32 matmul and the transpose /
+// row-broadcast-add / activation kernels around it (reference: lib/native/src/kernels/matmul.cuh:27-63,
+// lib/native/src/kernels/transpose.cuh:12-29, lib/native/src/kernels/elementwise.cuh:64-73).
+//
+// Structure of the tensor-core kernel (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: one elected lane streams 128xBK / BNxBK tiles into a STAGES-deep ring.
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128, N=BN, K=16) into one of two
+//               TMEM accumulators; tcgen05.commit releases smem stages and publishes accumulators.
+//   warps 2-5   epilogue: tcgen05.ld of the finished accumulator (one row per thread), bias /
+//               activation / residual / accumulate, bf16 or fp32 stores, while the issuer already
+//               works on the next tile in the other accumulator.
+#include <cuda_bf16.h>
+
+#include "common/host.h"
+#include "common/ptx.cuh"
+
+namespace dptb {
+
+__device__ int g_status[4] = {0, 0, 0, 0};
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* bias;       // [N], fp32 or bf16
+  int bias_f32;
+  const __nv_bfloat16* residual;  // [M, ldr]
+  long long ldr;
+  __nv_bfloat16* aux_out;         // pre-activation copy [M, ld_aux_out]
+  long long ld_aux_out;
+  const __nv_bfloat16* aux_in;    // pre-activation input for the derivative modes [M, ld_aux_in]
+  long long ld_aux_in;
+  int act;         // 0 none 1 relu 2 gelu_tanh 3 quick_gelu 4 silu | 11..14: multiply by act'(aux_in)
+  int out_f32;     // C is float
+  int accumulate;  // C += result
+  float alpha;
+  int vec_ok;      // all pointers 16-byte aligned and leading dimensions multiples of 8 elements
+  int tiles_m, tiles_n, num_kb;
+};
+
+// ----------------------------------------------------------------------------- epilogue math
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+__device__ __forceinline__ float act_fwd(int act, float x) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.0f);
+    case 2: {
+      float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanh_fast(u));
+    }
+    case 3: return x * sigmoid_fast(1.702f * x);
+    case 4: return x * sigmoid_fast(x);
+    default: return x;
+  }
+}
+__device__ __forceinline__ float act_bwd(int act, float x) {
+  switch (act) {
+    case 11: return x > 0.0f ? 1.0f : 0.0f;
+    case 12: {
+      float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      float t = tanh_fast(u);
+      return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+    }
+    case 13: {
+      float s = sigmoid_fast(1.702f * x);
+      return s + 1.702f * x * s * (1.0f - s);
+    }
+    case 14: {
+      float s = sigmoid_fast(x);
+      return s * (1.0f + x * (1.0f - s));
+    }
+    default: return 1.0f;
+  }
+}
+
+// One output element, used by the tail path of the tensor-core kernel and by the SIMT kernel.
+__device__ __forceinline__ void epilogue_scalar(const GemmParams& p, long long row, long long col, float v) {
+  v *= p.alpha;
+  if (p.bias) v += p.bias_f32 ? static_cast<const float*>(p.bias)[col] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
+  if (p.aux_out) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(v);
+  if (p.act >= 1 && p.act <= 4) v = act_fwd(p.act, v);
+  if (p.act >= 11) v *= act_bwd(p.act, __bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
+  if (p.residual) v += __bfloat162float(p.residual[row * p.ldr + col]);
+  if (p.out_f32) {
+    float* c = static_cast<float*>(p.C) + row * p.ldc + col;
+    *c = p.accumulate ? *c + v : v;
+  } else {
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+    *c = __float2bfloat16(p.accumulate ? __bfloat162float(*c) + v : v);
+  }
+}
+
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&out)[32]) {
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 u = s4[i];
+    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    out[i * 8 + 0] = a.x; out[i * 8 + 1] = a.y; out[i * 8 + 2] = b.x; out[i * 8 + 3] = b.y;
+    out[i * 8 + 4] = c.x; out[i * 8 + 5] = c.y; out[i * 8 + 6] = d.x; out[i * 8 + 7] = d.y;
+  }
+}
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32]) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 u;
+    u.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
+    u.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
+    u.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
+    u.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
+    d4[i] = u;
+  }
+}
+
+// 32 consecutive columns of one row, all in range and 16-byte aligned.
+__device__ __forceinline__ void epilogue_vec32(const GemmParams& p, long long row, long long col, float (&v)[32]) {
+  if (p.alpha != 1.0f) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+  }
+  if (p.bias) {
+    if (p.bias_f32) {
+      const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float4 b = __ldg(b4 + i);
+        v[i * 4 + 0] += b.x; v[i * 4 + 1] += b.y; v[i * 4 + 2] += b.z; v[i * 4 + 3] += b.w;
+      }
+    } else {
+      float b[32];
+      load_bf16x32(static_cast<const __nv_bfloat16*>(p.bias) + col, b);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] += b[i];
+    }
+  }
+  if (p.aux_out) store_bf16x32(p.aux_out + row * p.ld_aux_out + col, v);
+  if (p.act >= 1 && p.act <= 4) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = act_fwd(p.act, v[i]);
+  }
+  if (p.act >= 11) {
+    float pre[32];
+    load_bf16x32(p.aux_in + row * p.ld_aux_in + col, pre);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= act_bwd(p.act, pre[i]);
+  }
+  if (p.residual) {
+    float r[32];
+    load_bf16x32(p.residual + row * p.ldr + col, r);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += r[i];
+  }
+  if (p.out_f32) {
+    float4* c4 = reinterpret_cast<float4*>(static_cast<float*>(p.C) + row * p.ldc + col);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 o = make_float4(v[i * 4 + 0], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+      if (p.accumulate) {
+        float4 c = c4[i];
+        o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+      }
+      c4[i] = o;
+    }
+  } else {
+    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
+    if (p.accumulate) {
+      float old[32];
+      load_bf16x32(c, old);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] += old[i];
+    }
+    store_bf16x32(c, v);
+  }
+}
+
+// ----------------------------------------------------------------------------- tensor-core kernel
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBarOffset = STAGES * (kABytes + kBBytes);
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1) * 8 + 16 + 1024;  // + alignment slack
+};
+
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  constexpr int TMEM_COLS = 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * L::kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint64_t* drain_bar = tmem_empty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    if (lane == 0) {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], 1);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(&tmem_full[a], 1);
+        mbar_init(&tmem_empty[a], 4);
+      }
+      mbar_init(drain_bar, 1);
+      mbar_fence_init();
+    }
+    __syncwarp();
+    tmem_alloc<TMEM_COLS>(tmem_slot);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t issued = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * kBM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
+          const int s = issued % STAGES;
+          const uint32_t ph = (issued / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) break;
+          mbar_arrive_expect_tx(&full_bar[s], L::kABytes + L::kBBytes);
+          uint8_t* a_dst = sA + s * L::kABytes;
+          uint8_t* b_dst = sB + s * L::kBBytes;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + j * 64, kb * kBK);
+          } else {
+            tma_load_2d(a_dst, &tmA, &full_bar[s], kb * kBK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, kb * kBK);
+          } else {
+            tma_load_2d(b_dst, &tmB, &full_bar[s], kb * kBK, n0);
+          }
+        }
+      }
+      if (*abort_flag) {
+        // Do not leave while a tile copy may still be writing this CTA's shared memory.
+        const uint32_t n = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+        for (uint32_t j = 0; j < n; ++j) {
+          const uint32_t i = issued - 1 - j;
+          uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1)) {
+            if (global_timer_ns() - t0 > kWaitLimitNs / 4) {
+              report_error(kWaitDrainTimeout);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+      uint32_t consumed = 0;
+      uint32_t local_tile = 0;
+      bool issued_any = false;
+      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, kWaitTmemEmptyTimeout)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++consumed) {
+          const int s = consumed % STAGES;
+          const uint32_t ph = (consumed / STAGES) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, kWaitFullTimeout)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + s * L::kABytes);
+          const uint32_t b_addr = smem_u32(sB + s * L::kBBytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024) : make_smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          issued_any = true;
+          umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[acc]);  // accumulator complete
+      }
+      if (*abort_flag && issued_any) {
+        umma_commit(drain_bar);
+        uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(drain_bar, 0)) {
+          if (global_timer_ns() - t0 > kWaitLimitNs / 4) {
+            report_error(kWaitDrainTimeout);
+            break;
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
+      const int m0 = (tile % p.tiles_m) * kBM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout)) break;
+      tc_fence_after_sync();
+      const long long row = (long long)m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const long long col = (long long)n0 + c * 32;
+        if (col >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        if (row < p.M) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.vec_ok && col + 32 <= p.N) {
+            epilogue_vec32(p, row, col, v);
+          } else {
+            for (int i = 0; i < 32; ++i)
+              if (col + i < p.N) epilogue_scalar(p, row, col + i, v[i]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+}
+
+// ----------------------------------------------------------------------------- SIMT fallback
+// Any shape, any stride, fp32 or bf16 inputs.  64x64 tile, 16x16 threads, 4x4 outputs per thread.
+template <typename TA, typename TB>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const TA* __restrict__ A, long long sam, long long sak, const TB* __restrict__ B, long long sbk,
+                 long long sbn, const GemmParams p) {
+  __shared__ float As[16][64 + 1];
+  __shared__ float Bs[16][64 + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const long long m0 = (long long)blockIdx.y * 64, n0 = (long long)blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < p.K; k0 += 16) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      const int kk = i & 15, mm = i >> 4;
+      const long long m = m0 + mm, n = n0 + mm, k = k0 + kk;
+      As[kk][mm] = (m < p.M && k < p.K) ? (float)A[m * sam + k * sak] : 0.0f;
+      Bs[kk][mm] = (n < p.N && k < p.K) ? (float)B[k * sbk + n * sbn] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 4; ++j) {
+      const long long m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < p.M && n < p.N) epilogue_scalar(p, m, n, acc[i][j]);
+    }
+}
+
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace dptb
+
+using namespace dptb;
+
+// Argument block of dptb_gemm (mirrored by a ctypes.Structure in Python).
+struct DptbGemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  const void* bias;
+  const void* residual;
+  void* aux_out;
+  const void* aux_in;
+  long long lda, ldb, ldc, ldr, ld_aux_out, ld_aux_in;
+  int M, N, K;
+  int trans_a;   // 0: A stored [M, K] row-major; 1: A stored [K, M] row-major
+  int trans_b;   // 0: B stored [K, N] row-major; 1: B stored [N, K] row-major (nn.Linear weight)
+  int a_f32, b_f32;  // inputs are fp32 (SIMT path only)
+  int bias_f32, out_f32, accumulate, act;
+  float alpha;
+  int force_simt;
+  int bn;        // 0 = choose, else 128 or 256
+};
+
+extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (a->M <= 0 || a->N <= 0) return 0;
+  if (a->K < 0) return kErrBadShape;
+  GemmParams p;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.C = a->C; p.ldc = a->ldc;
+  p.bias = a->bias; p.bias_f32 = a->bias_f32;
+  p.residual = static_cast<const __nv_bfloat16*>(a->residual); p.ldr = a->ldr;
+  p.aux_out = static_cast<__nv_bfloat16*>(a->aux_out); p.ld_aux_out = a->ld_aux_out;
+  p.aux_in = static_cast<const __nv_bfloat16*>(a->aux_in); p.ld_aux_in = a->ld_aux_in;
+  p.act = a->act; p.out_f32 = a->out_f32; p.accumulate = a->accumulate; p.alpha = a->alpha;
+  if (p.act >= 11 && !p.aux_in) return kErrBadShape;
+
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  const bool tc_ok = !a->force_simt && !a->a_f32 && !a->b_f32 && a->K > 0 && al16(a->A) && al16(a->B) &&
+                     (a->lda % 8 == 0) && (a->ldb % 8 == 0);
+  p.vec_ok = al16(p.C) && (p.ldc % 8 == 0) && (!p.bias || al16(p.bias)) &&
+             (!p.residual || (al16(p.residual) && p.ldr % 8 == 0)) &&
+             (!p.aux_out || (al16(p.aux_out) && p.ld_aux_out % 8 == 0)) &&
+             (!p.aux_in || (al16(p.aux_in) && p.ld_aux_in % 8 == 0));
+
+  if (!tc_ok) {
+    p.tiles_m = p.tiles_n = p.num_kb = 0;
+    dim3 grid((unsigned)((a->N + 63) / 64), (unsigned)((a->M + 63) / 64));
+    const long long sam = a->trans_a ? 1 : a->lda, sak = a->trans_a ? a->lda : 1;
+    const long long sbk = a->trans_b ? 1 : a->ldb, sbn = a->trans_b ? a->ldb : 1;
+    if (a->a_f32 && a->b_f32)
+      gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)a->A, sam, sak, (const float*)a->B, sbk, sbn, p);
+    else if (!a->a_f32 && !a->b_f32)
+      gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a->A, sam, sak, (const __nv_bfloat16*)a->B, sbk, sbn, p);
+    else if (a->a_f32)
+      gemm_simt_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>((const float*)a->A, sam, sak, (const __nv_bfloat16*)a->B, sbk, sbn, p);
+    else
+      gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a->A, sam, sak, (const float*)a->B, sbk, sbn, p);
+    return (int)cudaGetLastError();
+  }
+
+  // Tile width: 256 when that still fills the machine, else 128.
+  int bn = a->bn;
+  if (bn != 128 && bn != 256) {
+    const long long t256 = (long long)((a->M + kBM - 1) / kBM) * ((a->N + 255) / 256);
+    bn = (a->N > 128 && t256 >= sm_count()) ? 256 : 128;
+  }
+  p.tiles_m = (a->M + kBM - 1) / kBM;
+  p.tiles_n = (a->N + bn - 1) / bn;
+  p.num_kb = (a->K + kBK - 1) / kBK;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (a->trans_a) rc = encode_tmap_2d_bf16(&tmA, a->A, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->lda * 2, 64, 64);
+  else            rc = encode_tmap_2d_bf16(&tmA, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda * 2, 64, kBM);
+  if (rc) return rc;
+  if (a->trans_b) rc = encode_tmap_2d_bf16(&tmB, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb * 2, 64, (uint32_t)bn);
+  else            rc = encode_tmap_2d_bf16(&tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb * 2, 64, 64);
+  if (rc) return rc;
+
+  const bool amn = a->trans_a != 0, bmn = a->trans_b == 0;
+#define DPTB_LAUNCH(AMN, BMN)                                                        \
+  (bn == 256 ? launch_tc<AMN, BMN, 256, 4>(tmA, tmB, p, stream) : launch_tc<AMN, BMN, 128, 6>(tmA, tmB, p, stream))
+  if (!amn && !bmn) return DPTB_LAUNCH(false, false);
+  if (!amn && bmn) return DPTB_LAUNCH(false, true);
+  if (amn && !bmn) return DPTB_LAUNCH(true, false);
+  return DPTB_LAUNCH(true, true);
+#undef DPTB_LAUNCH
+}
+
+// Status word access ------------------------------------------------------------------------------
+extern "C" int dptb_status_read(int* out4) {
+  return (int)cudaMemcpyFromSymbol(out4, g_status, sizeof(int) * 4);
+}
+extern "C" int dptb_status_clear() {
+  int z[4] = {0, 0, 0, 0};
+  return (int)cudaMemcpyToSymbol(g_status, z, sizeof(z));
+}

@@ -1,0 +1,446 @@
+"""Thin, allocation-explicit wrappers over the native kernels: torch tensors in, launch on the current stream.
+
+No autograd here (see ``ops/cuda.py``); these are the calls the autograd functions, the optimizers and the
+parallel layer share.  Every wrapper validates shapes on the host and raises on a non-zero return code.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+
+ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu_tanh": 2, "quick_gelu": 3, "silu": 4}
+ACT_BWD_CODES = {"relu": 11, "gelu_tanh": 12, "quick_gelu": 13, "silu": 14}
+
+
+def _lead(t: torch.Tensor) -> int:
+    """Leading dimension (elements) of a 2-D tensor whose last axis is contiguous."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError("expected a 2-D tensor with a contiguous last axis")
+    return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], t.stride(0))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+         bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         aux_out: Optional[torch.Tensor] = None, aux_in: Optional[torch.Tensor] = None, act=None,
+         act_bwd=None, accumulate: bool = False, alpha: float = 1.0, force_simt: bool = False, bn: int = 0,
+         n_cols: Optional[int] = None) -> torch.Tensor:
+    """``out[M,N] = epilogue(op(a) @ op(b))``.
+
+    ``a`` is stored ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is stored ``[K,N]`` (or ``[N,K]`` with ``trans_b``,
+    the layout of an ``nn.Linear`` weight).  All operands are 2-D with a contiguous last axis; row strides may exceed
+    the row length (padded buffers).  ``n_cols`` restricts N below ``out.shape[1]``.
+    Epilogue order: ``*alpha, +bias, aux_out<-value, act, *act'(aux_in), +residual, (+out)``.
+    """
+    lib = N.load()
+    if trans_a:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if trans_b:
+        Nn, Kb = b.shape
+    else:
+        Kb, Nn = b.shape
+    if n_cols is not None:
+        Nn = n_cols
+    if Kb != K:
+        raise ValueError(f"gemm: inner dimensions differ ({K} vs {Kb})")
+    if out.shape[0] != M or out.shape[1] < Nn:
+        raise ValueError(f"gemm: output is {tuple(out.shape)}, need [{M}, >={Nn}]")
+    args = N.GemmArgs()
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.lda, args.ldb, args.ldc = _lead(a), _lead(b), _lead(out)
+    args.M, args.N, args.K = M, Nn, K
+    args.trans_a, args.trans_b = int(trans_a), int(trans_b)
+    args.a_f32 = int(a.dtype == torch.float32)
+    args.b_f32 = int(b.dtype == torch.float32)
+    for t in (a, b):
+        if t.dtype not in (torch.float32, torch.bfloat16):
+            raise TypeError("gemm: inputs must be float32 or bfloat16")
+    args.out_f32 = int(out.dtype == torch.float32)
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("gemm: output must be float32 or bfloat16")
+    if bias is not None:
+        if bias.numel() < Nn:
+            raise ValueError("gemm: bias shorter than N")
+        args.bias = bias.data_ptr()
+        args.bias_f32 = int(bias.dtype == torch.float32)
+    for name, t in (("residual", residual), ("aux_out", aux_out), ("aux_in", aux_in)):
+        if t is not None:
+            if t.dtype != torch.bfloat16:
+                raise TypeError(f"gemm: {name} must be bfloat16")
+            if t.shape[0] != M or t.shape[1] < Nn:
+                raise ValueError(f"gemm: {name} has the wrong shape")
+    if residual is not None:
+        args.residual, args.ldr = residual.data_ptr(), _lead(residual)
+    if aux_out is not None:
+        args.aux_out, args.ld_aux_out = aux_out.data_ptr(), _lead(aux_out)
+    if aux_in is not None:
+        args.aux_in, args.ld_aux_in = aux_in.data_ptr(), _lead(aux_in)
+    args.act = ACT_BWD_CODES[act_bwd] if act_bwd else ACT_CODES[act]
+    args.accumulate = int(accumulate)
+    args.alpha = alpha
+    args.force_simt = int(force_simt)
+    args.bn = bn
+    N.check(lib.dptb_gemm(ctypes.byref(args), N.stream_ptr()), "gemm")
+    return out
+
+
+def norm_partial_rows() -> int:
+    """Rows of the ``[rows, 2, D]`` fp32 scratch the norm backward kernels need."""
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count * 2
+
+
+def layernorm_fwd(x, gamma, beta, eps):
+    lib = N.load()
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    rows = x2.shape[0]
+    y = torch.empty_like(x2)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    N.check(lib.dptb_layernorm_fwd(x2.data_ptr(), gamma.data_ptr(), N.ptr(beta), y.data_ptr(), mean.data_ptr(),
+                                   rstd.data_ptr(), rows, D, eps, N.dtype_code(x2), N.stream_ptr()), "layernorm_fwd")
+    return y.view(x.shape), mean, rstd
+
+
+def layernorm_bwd(x, dy, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, accumulate=False):
+    lib = N.load()
+    D = x.shape[-1]
+    x2, dy2 = x.reshape(-1, D), dy.reshape(-1, D)
+    rows = x2.shape[0]
+    dx = torch.empty_like(x2)
+    if dgamma is None:
+        dgamma = torch.empty_like(gamma)
+        accumulate = False
+    if dbeta is None:
+        dbeta = torch.empty_like(gamma)
+    prow = norm_partial_rows()
+    partial = torch.empty(prow * 2 * D, dtype=torch.float32, device=x.device)
+    N.check(lib.dptb_layernorm_bwd(x2.data_ptr(), dy2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+                                   N.ptr(None if dres is None else dres.reshape(-1, D)), dx.data_ptr(),
+                                   dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr(), prow, int(accumulate), rows,
+                                   D, N.dtype_code(x2), N.stream_ptr()), "layernorm_bwd")
+    return dx.view(x.shape), dgamma, dbeta
+
+
+def rmsnorm_fwd(x, gamma, eps):
+    lib = N.load()
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    rows = x2.shape[0]
+    y = torch.empty_like(x2)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    N.check(lib.dptb_rmsnorm_fwd(x2.data_ptr(), gamma.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, D, eps,
+                                 N.dtype_code(x2), N.stream_ptr()), "rmsnorm_fwd")
+    return y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(x, dy, gamma, rstd, dres=None, dgamma=None, accumulate=False):
+    lib = N.load()
+    D = x.shape[-1]
+    x2, dy2 = x.reshape(-1, D), dy.reshape(-1, D)
+    rows = x2.shape[0]
+    dx = torch.empty_like(x2)
+    if dgamma is None:
+        dgamma = torch.empty_like(gamma)
+        accumulate = False
+    prow = norm_partial_rows()
+    partial = torch.empty(prow * 2 * D, dtype=torch.float32, device=x.device)
+    N.check(lib.dptb_rmsnorm_bwd(x2.data_ptr(), dy2.data_ptr(), gamma.data_ptr(), rstd.data_ptr(),
+                                 N.ptr(None if dres is None else dres.reshape(-1, D)), dx.data_ptr(), dgamma.data_ptr(),
+                                 partial.data_ptr(), prow, int(accumulate), rows, D, N.dtype_code(x2), N.stream_ptr()),
+            "rmsnorm_bwd")
+    return dx.view(x.shape), dgamma
+
+
+def ce_fwd(logits2d: torch.Tensor, targets: torch.Tensor, vocab: int):
+    """Per-row loss and log-sum-exp over the first ``vocab`` columns of a (possibly padded) 2-D logits buffer."""
+    lib = N.load()
+    rows = logits2d.shape[0]
+    loss = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+    N.check(lib.dptb_ce_fwd(logits2d.data_ptr(), _lead(logits2d), targets.data_ptr(), loss.data_ptr(), lse.data_ptr(),
+                            rows, vocab, N.dtype_code(logits2d), N.stream_ptr()), "ce_fwd")
+    return loss, lse
+
+
+def ce_bwd(logits2d, targets, lse, g, scale: float, vocab: int, out=None, pad_to: Optional[int] = None):
+    """``(softmax - onehot) * g[row] * scale`` written to ``out`` (default: in place over ``logits2d``)."""
+    lib = N.load()
+    rows = logits2d.shape[0]
+    out = logits2d if out is None else out
+    pad_to = vocab if pad_to is None else pad_to
+    g_stride = 0 if g.numel() == 1 else 1
+    N.check(lib.dptb_ce_bwd(logits2d.data_ptr(), _lead(logits2d), targets.data_ptr(), lse.data_ptr(), g.data_ptr(),
+                            g_stride, scale, out.data_ptr(), _lead(out), rows, vocab, pad_to,
+                            N.dtype_code(logits2d), N.stream_ptr()), "ce_bwd")
+    return out
+
+
+def softmax_fwd(x):
+    lib = N.load()
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D).contiguous()
+    y = torch.empty_like(x2)
+    N.check(lib.dptb_softmax_fwd(x2.data_ptr(), y.data_ptr(), x2.shape[0], D, N.dtype_code(x2), N.stream_ptr()),
+            "softmax_fwd")
+    return y.view(x.shape)
+
+
+def softmax_bwd(y, dy):
+    lib = N.load()
+    D = y.shape[-1]
+    y2, dy2 = y.reshape(-1, D).contiguous(), dy.reshape(-1, D).contiguous()
+    dx = torch.empty_like(y2)
+    N.check(lib.dptb_softmax_bwd(y2.data_ptr(), dy2.data_ptr(), dx.data_ptr(), y2.shape[0], D, N.dtype_code(y2),
+                                 N.stream_ptr()), "softmax_bwd")
+    return dx.view(y.shape)
+
+
+def mean_f32(x: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    lib = N.load()
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    n = x.numel()
+    N.check(lib.dptb_mean_f32(x.data_ptr(), n, out.data_ptr(), (1.0 / n) if scale is None else scale, N.stream_ptr()),
+            "mean_f32")
+    return out
+
+
+def embedding_fwd(table, idx, pos_table=None, pos_start: int = 0, seq_len: int = 0):
+    lib = N.load()
+    idx = idx.contiguous()
+    n, D = idx.numel(), table.shape[1]
+    out = torch.empty(n, D, dtype=table.dtype, device=table.device)
+    N.check(lib.dptb_embedding_fwd(table.data_ptr(), table.shape[0], idx.data_ptr(), N.ptr(pos_table),
+                                   0 if pos_table is None else pos_table.shape[0], pos_start, seq_len, out.data_ptr(),
+                                   n, D, N.dtype_code(table), N.stream_ptr()), "embedding_fwd")
+    return out.view(*idx.shape, D)
+
+
+def embedding_bwd(dtable, idx, dout, deterministic: bool = True):
+    """``dtable[idx[n]] += dout[n]`` in place."""
+    lib = N.load()
+    idx = idx.reshape(-1).contiguous()
+    n, D = idx.numel(), dtable.shape[1]
+    dout2 = dout.reshape(n, D).contiguous()
+    sidx = perm = None
+    if deterministic:
+        sidx, perm = torch.sort(idx, stable=True)
+    N.check(lib.dptb_embedding_bwd(dtable.data_ptr(), dtable.shape[0], idx.data_ptr(), N.ptr(sidx), N.ptr(perm),
+                                   dout2.data_ptr(), n, D, N.dtype_code(dtable), N.stream_ptr()), "embedding_bwd")
+    return dtable
+
+
+def pos_embedding_bwd(dpos, dout, pos_start: int, seq_len: int, batch: int):
+    lib = N.load()
+    D = dpos.shape[1]
+    dout2 = dout.reshape(-1, D).contiguous()
+    N.check(lib.dptb_pos_embedding_bwd(dpos.data_ptr(), dpos.shape[0], pos_start, seq_len, batch, dout2.data_ptr(), D,
+                                       N.dtype_code(dpos), N.stream_ptr()), "pos_embedding_bwd")
+    return dpos
+
+
+def grad_norm(g_flat: torch.Tensor, ctrl: torch.Tensor, max_norm: float, partial: Optional[torch.Tensor] = None,
+              add_previous: bool = False):
+    """Global L2 norm of a flat gradient range into ``ctrl = [norm, scale, finite, sumsq]`` (fp32, device)."""
+    lib = N.load()
+    n = g_flat.numel()
+    parts = lib.dptb_sqnorm_parts(n)
+    if partial is None or partial.numel() < parts:
+        partial = torch.empty(parts, dtype=torch.float32, device=g_flat.device)
+    N.check(lib.dptb_grad_norm(g_flat.data_ptr(), n, N.dtype_code(g_flat), partial.data_ptr(), ctrl.data_ptr(),
+                               float(max_norm), int(add_previous), N.stream_ptr()), "grad_norm")
+    return ctrl
+
+
+def scale_by_ctrl(g_flat, ctrl):
+    lib = N.load()
+    N.check(lib.dptb_scale_by_ctrl(g_flat.data_ptr(), g_flat.numel(), N.dtype_code(g_flat), ctrl.data_ptr(),
+                                   N.stream_ptr()), "scale_by_ctrl")
+
+
+def adam_flat(p, shadow, g, m, v, ctrl, lr, beta1, beta2, eps, weight_decay, bc1, bc2, skip_if_nonfinite=False,
+              hyper=None):
+    lib = N.load()
+    N.check(lib.dptb_adam_flat(p.data_ptr(), N.ptr(shadow), g.data_ptr(), N.dtype_code(g), m.data_ptr(), v.data_ptr(),
+                               p.numel(), N.ptr(ctrl), lr, beta1, beta2, eps, weight_decay, bc1, bc2,
+                               int(skip_if_nonfinite), N.ptr(hyper), N.stream_ptr()), "adam_flat")
+
+
+def sgd_flat(p, shadow, g, buf, ctrl, lr, momentum, weight_decay, first_step):
+    lib = N.load()
+    N.check(lib.dptb_sgd_flat(p.data_ptr(), N.ptr(shadow), g.data_ptr(), N.dtype_code(g), N.ptr(buf), p.numel(),
+                              N.ptr(ctrl), lr, momentum, weight_decay, int(first_step), N.stream_ptr()), "sgd_flat")
+
+
+# --------------------------------------------------------------------------- elementwise / reductions / misc
+BINARY_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+UNARY_OPS = {"relu": 0, "sigmoid": 1, "tanh": 2, "abs": 3, "log": 4, "pow": 5, "gelu_tanh": 6, "quick_gelu": 7,
+             "silu": 8, "scale": 9, "exp": 10, "neg": 11, "sqrt": 12, "add_scalar": 13}
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, op: str) -> torch.Tensor:
+    """Same-shape, scalar (either side) or ``[M,N] op [N]`` row broadcast
+    (reference broadcast rules: lib/core/tensor/ops.dart:207-254)."""
+    lib = N.load()
+    a, b = a.contiguous(), b.contiguous()
+    if a.numel() == b.numel():
+        mode, big, cols = 0, a, 1
+    elif b.numel() == 1:
+        mode, big, cols = 1, a, 1
+    elif a.numel() == 1:
+        mode, big, cols = 3, b, 1
+    elif a.dim() >= 2 and b.numel() == a.shape[-1]:
+        mode, big, cols = 2, a, a.shape[-1]
+    else:
+        raise ValueError(f"binary {op}: shapes {tuple(a.shape)} and {tuple(b.shape)} do not broadcast")
+    out = torch.empty_like(big)
+    N.check(lib.dptb_binary(a.data_ptr(), b.data_ptr(), out.data_ptr(), big.numel(), cols, BINARY_OPS[op], mode,
+                            N.dtype_code(big), N.stream_ptr()), f"binary_{op}")
+    return out
+
+
+def unary(x: torch.Tensor, op: str, param: float = 0.0) -> torch.Tensor:
+    lib = N.load()
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    N.check(lib.dptb_unary(x.data_ptr(), out.data_ptr(), x.numel(), UNARY_OPS[op], float(param), N.dtype_code(x),
+                           N.stream_ptr()), f"unary_{op}")
+    return out
+
+
+def unary_bwd(x: torch.Tensor, dy: torch.Tensor, op: str, param: float = 0.0) -> torch.Tensor:
+    lib = N.load()
+    x, dy = x.contiguous(), dy.contiguous()
+    dx = torch.empty_like(x)
+    N.check(lib.dptb_unary_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(), UNARY_OPS[op], float(param),
+                               N.dtype_code(x), N.stream_ptr()), f"unary_bwd_{op}")
+    return dx
+
+
+def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False, n_cols=None):
+    """Column sums of a 2-D tensor (bias gradients), deterministic two-stage."""
+    lib = N.load()
+    rows = x2d.shape[0]
+    cols = x2d.shape[1] if n_cols is None else n_cols
+    if out is None:
+        out = torch.empty(cols, dtype=x2d.dtype, device=x2d.device)
+        accumulate = False
+    nparts = max(1, min(256, (rows + 63) // 64))
+    partial = torch.empty(nparts * cols, dtype=torch.float32, device=x2d.device)
+    N.check(lib.dptb_colsum(x2d.data_ptr(), _lead(x2d), out.data_ptr(), partial.data_ptr(), rows, cols, nparts,
+                            int(accumulate), N.dtype_code(x2d), N.stream_ptr()), "colsum")
+    return out
+
+
+def sum_all(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    lib = N.load()
+    x = x.contiguous()
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    partial = torch.empty(148 * 16 * 2, dtype=torch.float32, device=x.device)
+    N.check(lib.dptb_sum_all(x.data_ptr(), x.numel(), out.data_ptr(), partial.data_ptr(), float(scale),
+                             N.dtype_code(x), N.stream_ptr()), "sum_all")
+    return out
+
+
+def transpose2d(x: torch.Tensor) -> torch.Tensor:
+    lib = N.load()
+    x = x.contiguous()
+    rows, cols = x.shape
+    out = torch.empty(cols, rows, dtype=x.dtype, device=x.device)
+    N.check(lib.dptb_transpose2d(x.data_ptr(), out.data_ptr(), rows, cols, N.dtype_code(x), N.stream_ptr()),
+            "transpose2d")
+    return out
+
+
+def copy2d(src: torch.Tensor, dst: torch.Tensor, rows: int, cols: int):
+    lib = N.load()
+    N.check(lib.dptb_copy2d(src.data_ptr(), _lead(src), dst.data_ptr(), _lead(dst), rows, cols, N.dtype_code(src),
+                            N.stream_ptr()), "copy2d")
+    return dst
+
+
+def rope(x2d: torch.Tensor, heads: int, head_dim: int, rotary_dim: int, seq_len: int, pos_start: int, base: float,
+         inverse: bool = False, out: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+         col_offset: int = 0):
+    """Rotate ``heads`` consecutive heads starting at column ``col_offset`` of every row of ``x2d`` (row = token)."""
+    lib = N.load()
+    out = x2d if out is None else out
+    esz = x2d.element_size()
+    N.check(lib.dptb_rope(x2d.data_ptr() + col_offset * esz, out.data_ptr() + col_offset * esz, x2d.shape[0], heads,
+                          head_dim, rotary_dim, seq_len, pos_start, float(base), int(inverse), N.dtype_code(x2d),
+                          _lead(x2d), _lead(out), N.ptr(positions), N.stream_ptr()), "rope")
+    return out
+
+
+def dropout(x: torch.Tensor, p: float, seed: int, offset: int) -> torch.Tensor:
+    lib = N.load()
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    N.check(lib.dptb_dropout(x.data_ptr(), out.data_ptr(), x.numel(), float(p), seed, offset, N.dtype_code(x),
+                             N.stream_ptr()), "dropout")
+    return out
+
+
+def swiglu_fwd(g: torch.Tensor, u: torch.Tensor, out: Optional[torch.Tensor] = None):
+    lib = N.load()
+    rows, cols = g.shape
+    if out is None:
+        out = torch.empty(rows, cols, dtype=g.dtype, device=g.device)
+    N.check(lib.dptb_swiglu_fwd(g.data_ptr(), _lead(g), u.data_ptr(), _lead(u), out.data_ptr(), _lead(out), rows, cols,
+                                N.dtype_code(g), N.stream_ptr()), "swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(g, u, dout, dg, du):
+    lib = N.load()
+    rows, cols = g.shape
+    N.check(lib.dptb_swiglu_bwd(g.data_ptr(), _lead(g), u.data_ptr(), _lead(u), dout.data_ptr(), _lead(dout),
+                                dg.data_ptr(), _lead(dg), du.data_ptr(), _lead(du), rows, cols, N.dtype_code(g),
+                                N.stream_ptr()), "swiglu_bwd")
+    return dg, du
+
+
+def argmax_rows(x2d: torch.Tensor, n_cols: Optional[int] = None) -> torch.Tensor:
+    lib = N.load()
+    rows = x2d.shape[0]
+    cols = x2d.shape[1] if n_cols is None else n_cols
+    out = torch.empty(rows, dtype=torch.long, device=x2d.device)
+    N.check(lib.dptb_argmax_rows(x2d.data_ptr(), _lead(x2d), out.data_ptr(), rows, cols, N.dtype_code(x2d),
+                                 N.stream_ptr()), "argmax_rows")
+    return out
+
+
+def topk_sample(x2d: torch.Tensor, u: torch.Tensor, k: int, temperature: float, n_cols: Optional[int] = None):
+    lib = N.load()
+    rows = x2d.shape[0]
+    cols = x2d.shape[1] if n_cols is None else n_cols
+    out = torch.empty(rows, dtype=torch.long, device=x2d.device)
+    N.check(lib.dptb_topk_sample(x2d.data_ptr(), _lead(x2d), u.data_ptr(), out.data_ptr(), rows, cols, k,
+                                 float(temperature), N.dtype_code(x2d), 0, N.stream_ptr()), "topk_sample")
+    return out
+
+
+def im2col_nhwc(x: torch.Tensor, batch: int, channels: int, ksize: int, board: int = 8):
+    lib = N.load()
+    x = x.contiguous()
+    out = torch.empty(batch * board * board, channels * ksize * ksize, dtype=x.dtype, device=x.device)
+    N.check(lib.dptb_im2col_nhwc(x.data_ptr(), out.data_ptr(), batch, channels, ksize, board, N.dtype_code(x),
+                                 N.stream_ptr()), "im2col_nhwc")
+    return out
+
+
+def patchify(img: torch.Tensor, patch: int, out_dtype=None) -> torch.Tensor:
+    """``[B, C, H, W]`` image -> ``[B * (H/P) * (W/P), P*P*C]`` rows with per-patch order ``(dy, dx, c)``."""
+    lib = N.load()
+    img = img.contiguous()
+    B, C, H, W = img.shape
+    out_dtype = out_dtype or img.dtype
+    out = torch.empty(B * (H // patch) * (W // patch), patch * patch * C, dtype=out_dtype, device=img.device)
+    code = int(img.dtype == torch.bfloat16) + 2 * int(out_dtype == torch.bfloat16)
+    N.check(lib.dptb_patchify(img.data_ptr(), out.data_ptr(), B, C, H, W, patch, code, N.stream_ptr()), "patchify")
+    return out
