@@ -72,7 +72,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         for r in results:
             if r[2]:
                 print(r[2])
-    if rebuilt or not LIB.exists() or force:
+    stale = (not LIB.exists()) or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs)
+    if rebuilt or stale or force:
         cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(LIB),
                *[str(o) for o in objs], "-Xcompiler", "-fPIC"]
         proc = subprocess.run(cmd, capture_output=True, text=True)

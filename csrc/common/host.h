@@ -60,25 +60,26 @@ inline int encode_tmap_2d_bf16(CUtensorMap* map, const void* base, uint64_t inne
   return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
 }
 
-// 4-D bf16 tensor map with 128-byte swizzle: dims[0] is contiguous; strides[i] (bytes) is the stride of dims[i+1].
-inline int encode_tmap_4d_bf16(CUtensorMap* map, const void* base, const uint64_t dims_in[4],
-                               const uint64_t strides_bytes[3], const uint32_t box_in[4]) {
+// Rank-N (N <= 5) bf16 tensor map with 128-byte swizzle: dims[0] is contiguous; strides[i] (bytes) is the stride of
+// dims[i+1].  The rank must equal the dimensionality of the copy instruction that uses the map.
+inline int encode_tmap_nd_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims_in,
+                               const uint64_t* strides_bytes, const uint32_t* box_in) {
   EncodeTiledFn fn = get_encode_tiled();
   if (!fn) return kErrNoDriver;
-  if (reinterpret_cast<uintptr_t>(base) & 15) return kErrBadShape;
-  cuuint64_t dims[4];
-  cuuint64_t strides[3];
-  cuuint32_t box[4];
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  for (int i = 0; i < 4; ++i) {
+  if (rank < 1 || rank > 5 || (reinterpret_cast<uintptr_t>(base) & 15)) return kErrBadShape;
+  cuuint64_t dims[5];
+  cuuint64_t strides[4];
+  cuuint32_t box[5];
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
     dims[i] = dims_in[i];
     box[i] = box_in[i];
   }
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i + 1 < rank; ++i) {
     if (strides_bytes[i] & 15) return kErrBadShape;
     strides[i] = strides_bytes[i];
   }
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : kErrTensorMap;

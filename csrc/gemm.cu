@@ -340,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int n0 = (tile / p.tiles_m) * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
-      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout))) break;
       tc_fence_after_sync();
       const long long row = (long long)m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);

@@ -1,0 +1,88 @@
+"""GPU numerics of the tcgen05 attention kernels against the fp32 reference formula."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from dart_pytorch_b200.ops import flash as A
+from dart_pytorch_b200.ops import reference as R
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return float(((a - b).norm() / (b.norm() + 1e-12)).detach())
+
+
+def _qkv(B, S, H, Hkv, hd, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(B * S, (H + 2 * Hkv) * hd, device="cuda", generator=g).to(torch.bfloat16)
+
+
+def _split(qkv, B, S, H, Hkv, hd):
+    x = qkv.float().reshape(B, S, -1)
+    dq, dkv = H * hd, Hkv * hd
+    q = x[..., :dq].reshape(B, S, H, hd).transpose(1, 2)
+    k = x[..., dq:dq + dkv].reshape(B, S, Hkv, hd).transpose(1, 2)
+    v = x[..., dq + dkv:].reshape(B, S, Hkv, hd).transpose(1, 2)
+    return q, k, v
+
+
+FWD_CASES = [
+    # B, S, H, Hkv, hd, causal
+    (1, 128, 1, 1, 64, False), (1, 128, 1, 1, 64, True), (2, 256, 2, 2, 64, True), (2, 384, 3, 3, 64, True),
+    (2, 1024, 4, 4, 64, True), (3, 197, 2, 2, 64, False), (1, 300, 2, 1, 64, True), (2, 512, 4, 2, 64, False),
+    (1, 128, 1, 1, 128, True), (2, 256, 4, 1, 128, True), (1, 1000, 2, 2, 128, False),
+]
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,hd,causal", FWD_CASES)
+def test_attention_forward(B, S, H, Hkv, hd, causal):
+    qkv = _qkv(B, S, H, Hkv, hd)
+    dq, dkv = H * hd, Hkv * hd
+    o, lse = A.attn_fwd(qkv[:, :dq], qkv[:, dq:dq + dkv], qkv[:, dq + dkv:], B, S, S, H, Hkv, hd, causal)
+    q, k, v = _split(qkv, B, S, H, Hkv, hd)
+    ref = R.attention(q, k, v, causal=causal).transpose(1, 2).reshape(B * S, dq)
+    assert torch.isfinite(o.float()).all()
+    assert _rel(o, ref) < 2e-2
+    g = H // Hkv
+    s = (q @ k.repeat_interleave(g, 1).transpose(-1, -2)) / math.sqrt(hd)
+    if causal:
+        s = s + torch.triu(torch.full((S, S), float("-inf"), device="cuda"), 1)
+    assert _rel(lse, torch.logsumexp(s, -1)) < 1e-3
+
+
+def test_attention_forward_q_offset():
+    B, Sq, Sk, H, hd = 2, 128, 384, 2, 64
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q2 = torch.randn(B * Sq, H * hd, device="cuda", generator=g).bfloat16()
+    k2 = torch.randn(B * Sk, H * hd, device="cuda", generator=g).bfloat16()
+    v2 = torch.randn(B * Sk, H * hd, device="cuda", generator=g).bfloat16()
+    o, _ = A.attn_fwd(q2, k2, v2, B, Sq, Sk, H, H, hd, True, q_offset=Sk - Sq)
+    q = q2.float().reshape(B, Sq, H, hd).transpose(1, 2)
+    k = k2.float().reshape(B, Sk, H, hd).transpose(1, 2)
+    v = v2.float().reshape(B, Sk, H, hd).transpose(1, 2)
+    ref = R.attention(q, k, v, causal=True, q_offset=Sk - Sq).transpose(1, 2).reshape(B * Sq, H * hd)
+    assert _rel(o, ref) < 2e-2
+
+
+BWD_CASES = [(1, 128, 1, 1, 64, False), (1, 128, 1, 1, 64, True), (2, 256, 2, 2, 64, True), (2, 640, 3, 3, 64, True),
+             (3, 197, 2, 2, 64, False), (1, 300, 4, 2, 64, True), (2, 1024, 2, 2, 64, True)]
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,hd,causal", BWD_CASES)
+def test_attention_backward(B, S, H, Hkv, hd, causal):
+    qkv = _qkv(B, S, H, Hkv, hd).requires_grad_(True)
+    o = A.attention_packed(qkv, B, S, H, Hkv, hd, causal)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    do = torch.randn(o.shape, device="cuda", generator=g).bfloat16()
+    o.backward(do)
+    x = qkv.detach().float().requires_grad_(True)
+    q, k, v = _split(x, B, S, H, Hkv, hd)
+    ref = R.attention(q, k, v, causal=causal).transpose(1, 2).reshape(B * S, H * hd)
+    ref.backward(do.float())
+    dq_, dkv_ = H * hd, Hkv * hd
+    for name, sl in (("dq", slice(0, dq_)), ("dk", slice(dq_, dq_ + dkv_)), ("dv", slice(dq_ + dkv_, None))):
+        assert torch.isfinite(qkv.grad[:, sl].float()).all(), name
+        assert _rel(qkv.grad[:, sl], x.grad[:, sl]) < 3e-2, name
