@@ -484,5 +484,5 @@ extern "C" int dptb_attn_bwd(const DptbAttnBwdArgs* a, void* stream) {
   long long cgrid = (rows * (cols / 4) + 255) / 256;
   if (cgrid > sm_count() * 16) cgrid = sm_count() * 16;
   attn_dq_convert_kernel<<<(int)cgrid, 256, 0, st>>>(a->dq_acc, static_cast<__nv_bfloat16*>(a->dq), a->lddq, rows, cols);
-  return (int)cudaGetLastError();
+  return counted(3, (int)cudaGetLastError());
 }

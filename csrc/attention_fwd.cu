@@ -441,7 +441,7 @@ static int attn_fwd_launch(const DptbAttnFwdArgs* a, cudaStream_t st) {
   DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   dim3 grid(p.num_q_blocks, a->Hq, a->B);
   kern<<<grid, kAttnThreads, L::kTotal, st>>>(tmQ, tmK, tmV, p);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 
 extern "C" int dptb_attn_fwd(const DptbAttnFwdArgs* a, void* stream) {

@@ -85,6 +85,16 @@ inline int encode_tmap_nd_bf16(CUtensorMap* map, const void* base, int rank, con
   return r == CUDA_SUCCESS ? 0 : kErrTensorMap;
 }
 
+// Number of kernels this library has launched since the last reset (host-side bookkeeping for benchmarks).
+inline long long& launch_counter() {
+  static long long count = 0;
+  return count;
+}
+inline int counted(int kernels, int rc) {
+  if (rc == 0) launch_counter() += kernels;
+  return rc;
+}
+
 inline int sm_count() {
   static int cached[16] = {0};
   int dev = 0;

@@ -436,7 +436,7 @@ extern "C" int dptb_binary(const void* a, const void* b, void* out, long long n,
   DPTB_BY_DTYPE(dtype,
                 (binary_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n, cols, op, bmode)),
                 (binary_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)a, (const float*)b, (float*)out, n, cols, op, bmode)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_unary(const void* x, void* out, long long n, int op, float param, int dtype, void* stream) {
   if (n <= 0) return 0;
@@ -444,7 +444,7 @@ extern "C" int dptb_unary(const void* x, void* out, long long n, int op, float p
   DPTB_BY_DTYPE(dtype,
                 (unary_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, op, param)),
                 (unary_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)x, (float*)out, n, op, param)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_unary_bwd(const void* x, const void* dy, void* dx, long long n, int op, float param, int dtype,
                               void* stream) {
@@ -453,7 +453,7 @@ extern "C" int dptb_unary_bwd(const void* x, const void* dy, void* dx, long long
   DPTB_BY_DTYPE(dtype,
                 (unary_bwd_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, n, op, param)),
                 (unary_bwd_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)x, (const float*)dy, (float*)dx, n, op, param)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 // partial: fp32 scratch of nparts * cols floats; out has `out_dtype` (0 fp32, 1 bf16).
 extern "C" int dptb_colsum(const void* x, long long ld, void* out, float* partial, long long rows, int cols, int nparts,
@@ -469,7 +469,7 @@ extern "C" int dptb_colsum(const void* x, long long ld, void* out, float* partia
   DPTB_BY_DTYPE(dtype,
                 (colsum_final_kernel<__nv_bfloat16><<<(cols + 255) / 256, 256, 0, st>>>(partial, nparts, cols, (__nv_bfloat16*)out, accumulate)),
                 (colsum_final_kernel<float><<<(cols + 255) / 256, 256, 0, st>>>(partial, nparts, cols, (float*)out, accumulate)));
-  return (int)cudaGetLastError();
+  return counted(2, (int)cudaGetLastError());
 }
 // partial: fp32 scratch of at least 148*16 floats.
 extern "C" int dptb_sum_all(const void* x, long long n, float* out, float* partial, float scale, int dtype, void* stream) {
@@ -480,7 +480,7 @@ extern "C" int dptb_sum_all(const void* x, long long n, float* out, float* parti
                 (sum_partial_kernel<float><<<parts, kEwThreads, 0, st>>>((const float*)x, n, partial)));
   DPTB_CUDA_OK(cudaGetLastError());
   sum_final_kernel<<<1, 1024, 0, st>>>(partial, parts, out, scale);
-  return (int)cudaGetLastError();
+  return counted(2, (int)cudaGetLastError());
 }
 extern "C" int dptb_transpose2d(const void* in, void* out, long long rows, long long cols, int dtype, void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
@@ -489,7 +489,7 @@ extern "C" int dptb_transpose2d(const void* in, void* out, long long rows, long 
   DPTB_BY_DTYPE(dtype,
                 (transpose_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, cols)),
                 (transpose_kernel<float><<<grid, 256, 0, st>>>((const float*)in, (float*)out, rows, cols)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_copy2d(const void* src, long long lds, void* dst, long long ldd, long long rows, long long cols,
                            int dtype, void* stream) {
@@ -498,7 +498,7 @@ extern "C" int dptb_copy2d(const void* src, long long lds, void* dst, long long 
   DPTB_BY_DTYPE(dtype,
                 (copy2d_kernel<__nv_bfloat16><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const __nv_bfloat16*)src, lds, (__nv_bfloat16*)dst, ldd, rows, cols)),
                 (copy2d_kernel<float><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const float*)src, lds, (float*)dst, ldd, rows, cols)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_rope(const void* x, void* out, long long tokens, int heads, int head_dim, int rotary_dim,
                          int seq_len, int pos_start, float base, int inverse, int dtype, long long ld_in,
@@ -517,7 +517,7 @@ extern "C" int dptb_rope(const void* x, void* out, long long tokens, int heads, 
                   (rope_tail_kernel<__nv_bfloat16><<<ew_grid(nt), kEwThreads, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, tokens, heads, head_dim, rotary_dim, ld_in, ld_out)),
                   (rope_tail_kernel<float><<<ew_grid(nt), kEwThreads, 0, st>>>((const float*)x, (float*)out, tokens, heads, head_dim, rotary_dim, ld_in, ld_out)));
   }
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_dropout(const void* x, void* out, long long n, float p, unsigned long long seed,
                             unsigned long long offset, int dtype, void* stream) {
@@ -526,7 +526,7 @@ extern "C" int dptb_dropout(const void* x, void* out, long long n, float p, unsi
   DPTB_BY_DTYPE(dtype,
                 (dropout_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, p, seed, offset)),
                 (dropout_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)x, (float*)out, n, p, seed, offset)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_swiglu_fwd(const void* g, long long ldg, const void* u, long long ldu, void* out, long long ldo,
                                long long rows, int cols, int dtype, void* stream) {
@@ -535,7 +535,7 @@ extern "C" int dptb_swiglu_fwd(const void* g, long long ldg, const void* u, long
   DPTB_BY_DTYPE(dtype,
                 (swiglu_fwd_kernel<__nv_bfloat16><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)out, ldo, rows, cols)),
                 (swiglu_fwd_kernel<float><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (float*)out, ldo, rows, cols)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_swiglu_bwd(const void* g, long long ldg, const void* u, long long ldu, const void* dout,
                                long long ldo, void* dg, long long lddg, void* du, long long lddu, long long rows,
@@ -545,7 +545,7 @@ extern "C" int dptb_swiglu_bwd(const void* g, long long ldg, const void* u, long
   DPTB_BY_DTYPE(dtype,
                 (swiglu_bwd_kernel<__nv_bfloat16><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)dout, ldo, (__nv_bfloat16*)dg, lddg, (__nv_bfloat16*)du, lddu, rows, cols)),
                 (swiglu_bwd_kernel<float><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (const float*)dout, ldo, (float*)dg, lddg, (float*)du, lddu, rows, cols)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_argmax_rows(const void* x, long long ld, long long* out, long long rows, int cols, int dtype,
                                 void* stream) {
@@ -555,7 +555,7 @@ extern "C" int dptb_argmax_rows(const void* x, long long ld, long long* out, lon
   DPTB_BY_DTYPE(dtype,
                 (argmax_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, out, rows, cols)),
                 (argmax_rows_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ld, out, rows, cols)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_topk_sample(const void* x, long long ld, const float* u, long long* out, long long rows, int cols,
                                 int k, float temperature, int dtype, int reserved, void* stream) {
@@ -568,7 +568,7 @@ extern "C" int dptb_topk_sample(const void* x, long long ld, const float* u, lon
   DPTB_BY_DTYPE(dtype,
                 (topk_sample_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, u, out, rows, cols, k, temperature)),
                 (topk_sample_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ld, u, out, rows, cols, k, temperature)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_im2col_nhwc(const void* in, void* out, int batch, int channels, int ksize, int board, int dtype,
                                 void* stream) {
@@ -578,7 +578,7 @@ extern "C" int dptb_im2col_nhwc(const void* in, void* out, int batch, int channe
   DPTB_BY_DTYPE(dtype,
                 (im2col_nhwc_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, batch, channels, ksize, board)),
                 (im2col_nhwc_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)in, (float*)out, batch, channels, ksize, board)));
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 // in_dtype / out_dtype packed as dtype = in + 2*out.
 extern "C" int dptb_patchify(const void* img, void* out, int B, int C, int H, int W, int P, int dtype, void* stream) {
@@ -591,5 +591,5 @@ extern "C" int dptb_patchify(const void* img, void* out, int B, int C, int H, in
   else if (!in_bf && out_bf) patchify_kernel<float, __nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)img, (__nv_bfloat16*)out, B, C, H, W, P);
   else if (!in_bf && !out_bf) patchify_kernel<float, float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)img, (float*)out, B, C, H, W, P);
   else patchify_kernel<__nv_bfloat16, float><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)img, (float*)out, B, C, H, W, P);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }

@@ -126,7 +126,7 @@ extern "C" int dptb_embedding_fwd(const void* table, long long vocab, const long
                                         reinterpret_cast<uintptr_t>(out)) & 15) == 0);
   if (dtype) embedding_fwd_kernel<__nv_bfloat16><<<warp_grid(n), 256, 0, st>>>((const __nv_bfloat16*)table, vocab, idx, (const __nv_bfloat16*)pos_table, pos_rows, pos_start, seq_len, (__nv_bfloat16*)out, n, D, vec_ok);
   else       embedding_fwd_kernel<float><<<warp_grid(n), 256, 0, st>>>((const float*)table, vocab, idx, (const float*)pos_table, pos_rows, pos_start, seq_len, (float*)out, n, D, vec_ok);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 // sorted_idx / perm may be null: then the atomic form runs.
 extern "C" int dptb_embedding_bwd(void* dtable, long long vocab, const long long* idx, const long long* sorted_idx,
@@ -140,7 +140,7 @@ extern "C" int dptb_embedding_bwd(void* dtable, long long vocab, const long long
     if (dtype) embedding_bwd_atomic_kernel<__nv_bfloat16><<<warp_grid(n), 256, 0, st>>>((__nv_bfloat16*)dtable, vocab, idx, (const __nv_bfloat16*)dout, n, D);
     else       embedding_bwd_atomic_kernel<float><<<warp_grid(n), 256, 0, st>>>((float*)dtable, vocab, idx, (const float*)dout, n, D);
   }
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_pos_embedding_bwd(void* dpos, long long pos_rows, int pos_start, int seq_len, long long batch,
                                       const void* dout, int D, int dtype, void* stream) {
@@ -151,5 +151,5 @@ extern "C" int dptb_pos_embedding_bwd(void* dpos, long long pos_rows, int pos_st
   if (blocks > sm_count() * 8) blocks = sm_count() * 8;
   if (dtype) pos_embedding_bwd_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)dpos, pos_rows, pos_start, seq_len, batch, (const __nv_bfloat16*)dout, D);
   else       pos_embedding_bwd_kernel<float><<<blocks, 256, 0, st>>>((float*)dpos, pos_rows, pos_start, seq_len, batch, (const float*)dout, D);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }

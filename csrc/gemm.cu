@@ -429,7 +429,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmP
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 
 }  // namespace dptb
@@ -491,7 +491,7 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
       gemm_simt_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>((const float*)a->A, sam, sak, (const __nv_bfloat16*)a->B, sbk, sbn, p);
     else
       gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a->A, sam, sak, (const float*)a->B, sbk, sbn, p);
-    return (int)cudaGetLastError();
+    return counted(1, (int)cudaGetLastError());
   }
 
   // Tile width: 256 when that still fills the machine, else 128.
@@ -531,3 +531,6 @@ extern "C" int dptb_status_clear() {
   int z[4] = {0, 0, 0, 0};
   return (int)cudaMemcpyToSymbol(g_status, z, sizeof(z));
 }
+
+extern "C" long long dptb_launch_count() { return launch_counter(); }
+extern "C" void dptb_launch_count_reset() { launch_counter() = 0; }

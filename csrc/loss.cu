@@ -181,7 +181,7 @@ extern "C" int dptb_ce_fwd(const void* logits, long long ld, const long long* ta
   const int vec_ok = ((reinterpret_cast<uintptr_t>(logits) & 15) == 0) && (ld % 8 == 0);
   if (dtype) ce_fwd_kernel<__nv_bfloat16><<<row_grid(rows), kLossThreads, 0, st>>>((const __nv_bfloat16*)logits, ld, targets, loss, lse, rows, V, vec_ok);
   else       ce_fwd_kernel<float><<<row_grid(rows), kLossThreads, 0, st>>>((const float*)logits, ld, targets, loss, lse, rows, V, vec_ok);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 // pad_to: number of leading columns of each dlogits row to write (V <= pad_to <= ldd); columns in [V, pad_to) get 0.
 extern "C" int dptb_ce_bwd(const void* logits, long long ld, const long long* targets, const float* lse, const float* g,
@@ -194,23 +194,23 @@ extern "C" int dptb_ce_bwd(const void* logits, long long ld, const long long* ta
                      (ld % 8 == 0) && (ldd % 8 == 0) && (pad_to % 8 == 0);
   if (dtype) ce_bwd_kernel<__nv_bfloat16><<<row_grid(rows), kLossThreads, 0, st>>>((const __nv_bfloat16*)logits, ld, targets, lse, g, g_stride, scale, (__nv_bfloat16*)dlogits, ldd, rows, V, pad_to, vec_ok);
   else       ce_bwd_kernel<float><<<row_grid(rows), kLossThreads, 0, st>>>((const float*)logits, ld, targets, lse, g, g_stride, scale, (float*)dlogits, ldd, rows, V, pad_to, vec_ok);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_softmax_fwd(const void* x, void* y, long long rows, int D, int dtype, void* stream) {
   if (rows <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
   if (dtype) softmax_fwd_kernel<__nv_bfloat16><<<row_grid(rows), kLossThreads, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, rows, D);
   else       softmax_fwd_kernel<float><<<row_grid(rows), kLossThreads, 0, st>>>((const float*)x, (float*)y, rows, D);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_softmax_bwd(const void* y, const void* dy, void* dx, long long rows, int D, int dtype, void* stream) {
   if (rows <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
   if (dtype) softmax_bwd_kernel<__nv_bfloat16><<<row_grid(rows), kLossThreads, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, rows, D);
   else       softmax_bwd_kernel<float><<<row_grid(rows), kLossThreads, 0, st>>>((const float*)y, (const float*)dy, (float*)dx, rows, D);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_mean_f32(const float* x, long long n, float* out, float scale, void* stream) {
   mean_f32_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(x, n, out, scale);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }

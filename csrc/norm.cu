@@ -315,7 +315,7 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
     long long blocks = rows < nsm * 8 ? rows : nsm * 8;
     norm_fwd_generic_kernel<T, RMS><<<(int)blocks, kNormThreads, 0, st>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps);
   }
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 
 template <typename T, bool RMS>
@@ -347,7 +347,7 @@ static int norm_bwd_launch(const void* x, const void* dy, const void* gamma, con
   }
   DPTB_CUDA_OK(cudaGetLastError());
   norm_param_grad_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(partial, blocks, D, (T*)dgamma, RMS ? (T*)nullptr : (T*)dbeta, accumulate);
-  return (int)cudaGetLastError();
+  return counted(2, (int)cudaGetLastError());
 }
 
 }  // namespace dptb

@@ -167,13 +167,13 @@ extern "C" int dptb_grad_norm(const void* g, long long n, int gdtype, float* par
   else        sqnorm_partial_kernel<float><<<parts, kOptThreads, 0, st>>>((const float*)g, n, partial);
   DPTB_CUDA_OK(cudaGetLastError());
   clip_finalize_kernel<<<1, 1024, 0, st>>>(partial, parts, ctrl, max_norm, add_previous);
-  return (int)cudaGetLastError();
+  return counted(2, (int)cudaGetLastError());
 }
 extern "C" int dptb_scale_by_ctrl(void* g, long long n, int gdtype, const float* ctrl, void* stream) {
   auto st = static_cast<cudaStream_t>(stream);
   if (gdtype) scale_by_ctrl_kernel<__nv_bfloat16><<<flat_grid(n, 1), kOptThreads, 0, st>>>((__nv_bfloat16*)g, n, ctrl);
   else        scale_by_ctrl_kernel<float><<<flat_grid(n, 1), kOptThreads, 0, st>>>((float*)g, n, ctrl);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_adam_flat(float* p, void* shadow, const void* g, int gdtype, float* m, float* v, long long n,
                               const float* ctrl, float lr, float beta1, float beta2, float eps, float weight_decay,
@@ -187,7 +187,7 @@ extern "C" int dptb_adam_flat(float* p, void* shadow, const void* g, int gdtype,
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, skip_if_nonfinite, hyper};
   if (gdtype) adam_flat_kernel<__nv_bfloat16><<<flat_grid(n, 8), kOptThreads, 0, st>>>(p, (__nv_bfloat16*)shadow, (const __nv_bfloat16*)g, m, v, n, ctrl, a);
   else        adam_flat_kernel<float><<<flat_grid(n, 8), kOptThreads, 0, st>>>(p, (__nv_bfloat16*)shadow, (const float*)g, m, v, n, ctrl, a);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_sgd_flat(float* p, void* shadow, const void* g, int gdtype, float* buf, long long n,
                              const float* ctrl, float lr, float momentum, float weight_decay, int first_step,
@@ -196,5 +196,5 @@ extern "C" int dptb_sgd_flat(float* p, void* shadow, const void* g, int gdtype, 
   auto st = static_cast<cudaStream_t>(stream);
   if (gdtype) sgd_flat_kernel<__nv_bfloat16><<<flat_grid(n, 1), kOptThreads, 0, st>>>(p, (__nv_bfloat16*)shadow, (const __nv_bfloat16*)g, buf, n, ctrl, lr, momentum, weight_decay, first_step);
   else        sgd_flat_kernel<float><<<flat_grid(n, 1), kOptThreads, 0, st>>>(p, (__nv_bfloat16*)shadow, (const float*)g, buf, n, ctrl, lr, momentum, weight_decay, first_step);
-  return (int)cudaGetLastError();
+  return counted(1, (int)cudaGetLastError());
 }

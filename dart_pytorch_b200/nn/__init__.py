@@ -1,0 +1,9 @@
+"""Neural-network building blocks (reference: lib/core/nn/*.dart)."""
+from .module import Module, make_param
+from .layers import (Linear, LayerNorm, RMSNorm, Embedding, Dropout, SinusoidalPositionalEncoding,
+                     LearnedPositionalEmbedding, SwiGluFfn, VisionProjector, causal_mask, activation_name)
+from .attention import RopeCache, MHACache, EncoderCache, MultiHeadAttention, MultiHeadCrossAttention
+from .transformer import (Activation, TransformerBlock, TransformerEncoder, TransformerDecoderBlock,
+                          TransformerDecoder)
+
+causalMask = causal_mask

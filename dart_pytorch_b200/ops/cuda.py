@@ -500,3 +500,24 @@ class SwiGLUFn(torch.autograd.Function):
         d = torch.empty_like(gu2)
         K.swiglu_bwd(gu2[:, :F], gu2[:, F:], _as2d(dout), d[:, :F], d[:, F:])
         return d.view(ctx.shape)
+
+
+class RopeColsFn(torch.autograd.Function):
+    """In-place rotary embedding of the first ``heads`` head blocks of every row of a fused projection output
+    (the Q and K columns of ``[rows, (H + 2 Hkv) hd]``); the V columns are untouched.  The backward applies the inverse
+    rotation to the same columns of the incoming gradient, also in place (that gradient is produced by the attention
+    backward and has no other consumer)."""
+
+    @staticmethod
+    def forward(ctx, qkv, heads, head_dim, rotary_dim, seq_len, pos_start, base):
+        K.rope(qkv, heads, head_dim, rotary_dim, seq_len, pos_start, base)
+        ctx.mark_dirty(qkv)
+        ctx.cfg = (heads, head_dim, rotary_dim, seq_len, pos_start, base)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dy):
+        heads, head_dim, rotary_dim, seq_len, pos_start, base = ctx.cfg
+        d = dy if dy.is_contiguous() else dy.contiguous()
+        K.rope(d, heads, head_dim, rotary_dim, seq_len, pos_start, base, inverse=True)
+        return d, None, None, None, None, None, None

@@ -1,0 +1,78 @@
+"""Adam with decoupled weight decay (reference: lib/core/optim/adam.dart:18-124).
+
+``m = b1 m + (1-b1) g``; ``v = b2 v + (1-b2) g^2``; ``update = lr * (m / (1-b1^t)) / (sqrt(v / (1-b2^t)) + eps)``;
+``update += lr * wd * p`` (decay applied to every parameter, as the reference does); parameters without a gradient are
+skipped.  On the device this is one kernel over the arena: it reads the bf16 gradient (times the pending clip
+coefficient), updates fp32 master / m / v and rewrites the bf16 working copy."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .optimizer import Optimizer
+
+
+class Adam(Optimizer):
+    def __init__(self, parameters, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                 weight_decay: float = 0.0, weightDecay=None, arena=None, skip_nonfinite: bool = False):
+        super().__init__(parameters, lr, arena)
+        self.beta1, self.beta2, self.eps = float(beta1), float(beta2), float(eps)
+        self.weight_decay = float(weight_decay if weightDecay is None else weightDecay)
+        self.skip_nonfinite = skip_nonfinite
+        self._step = 0
+        self._m, self._v = {}, {}
+        if self.arena is not None:
+            n, dev = self.arena.numel, self.arena.device
+            self.m = torch.zeros(n, dtype=torch.float32, device=dev)
+            self.v = torch.zeros(n, dtype=torch.float32, device=dev)
+            # {lr, 1-b1^t, 1-b2^t} read by the kernel from device memory, so a captured graph sees fresh values.
+            self.hyper = torch.zeros(4, dtype=torch.float32, device=dev)
+            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+
+    @property
+    def step_count(self) -> int:
+        return self._step
+
+    def prepare_step(self) -> None:
+        """Host half of a device step: advance ``t`` and publish {lr, bias corrections} to the device (async copy).
+        Call outside a CUDA-graph capture; ``launch_step`` is the capturable half."""
+        self._step += 1
+        self._hyper_host[0] = self.lr
+        self._hyper_host[1] = 1.0 - self.beta1 ** self._step
+        self._hyper_host[2] = 1.0 - self.beta2 ** self._step
+        self.hyper.copy_(self._hyper_host, non_blocking=True)
+
+    def launch_step(self) -> None:
+        from ..ops import kernels as K
+        a = self.arena
+        master = a.master if a.master is not None else a.flat
+        shadow = a.flat if a.master is not None else None
+        K.adam_flat(master, shadow, a.grad, self.m, self.v, self._grad_ctrl(), self.lr, self.beta1, self.beta2, self.eps,
+                    self.weight_decay, 1.0, 1.0, skip_if_nonfinite=self.skip_nonfinite, hyper=self.hyper)
+        self.clip_pending = False
+
+    def step(self) -> None:
+        if self.arena is not None:
+            self.prepare_step()
+            self.launch_step()
+            return
+        self._step += 1
+        bc1 = 1.0 - self.beta1 ** self._step
+        bc2 = 1.0 - self.beta2 ** self._step
+        with torch.no_grad():
+            for p in self.parameters:
+                if p.grad is None:
+                    continue
+                g = p.grad
+                m = self._m.get(id(p))
+                v = self._v.get(id(p))
+                if m is None:
+                    m, v = torch.zeros_like(p), torch.zeros_like(p)
+                m = self.beta1 * m + (1.0 - self.beta1) * g
+                v = self.beta2 * v + (1.0 - self.beta2) * g * g
+                self._m[id(p)], self._v[id(p)] = m, v
+                update = self.lr * (m / bc1) / (torch.sqrt(v / bc2) + self.eps)
+                if self.weight_decay != 0.0:
+                    update = update + self.lr * self.weight_decay * p
+                p.sub_(update)
