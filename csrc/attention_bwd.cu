@@ -370,26 +370,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b, h, s] = sum_d dO * O over one head row; one warp per (row, head).
+// delta[b, h, s] = sum_d dO * O over one head row of 64 values: 8 lanes per (token, head), 16 bytes per lane, so a
+// warp reads four consecutive heads of a token as one 512-byte run.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo, const __nv_bfloat16* __restrict__ dout,
                   long long lddo, float* __restrict__ delta, int B, int S, int H, int hd) {
-  const int lane = threadIdx.x & 31;
+  const int sub = threadIdx.x & 7;
   const long long total = (long long)B * S * H;
-  for (long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); w < total; w += (long long)gridDim.x * 8) {
+  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3; w < total;
+       w += ((long long)gridDim.x * blockDim.x) >> 3) {
     const int h = (int)(w % H);
     const long long tok = w / H;  // b*S + s
-    float acc = 0.0f;
-    for (int d = lane * 2; d < hd; d += 64) {
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + tok * ldo + (long long)h * hd + d));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dout + tok * lddo + (long long)h * hd + d));
-      acc += a.x * b.x + a.y * b.y;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) {
-      const long long b = tok / S, s = tok % S;
-      delta[(b * H + h) * S + s] = acc;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + tok * ldo + (long long)h * hd + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + tok * lddo + (long long)h * hd + sub * 8);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+    const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
+    float acc = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x +
+                a3.y * b3.y;
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    if (sub == 0) {
+      const long long bb = tok / S, ss = tok % S;
+      delta[(bb * H + h) * S + ss] = acc;
     }
   }
 }
@@ -451,8 +454,8 @@ extern "C" int dptb_attn_bwd(const DptbAttnBwdArgs* a, void* stream) {
         reinterpret_cast<uintptr_t>(a->dq_acc)) & 15) != 0)
     return kErrBadShape;
   using L = AttnBwdSmem;
-  const long long warps = (long long)a->B * a->Sq * a->Hq;
-  int dgrid = (int)((warps + 7) / 8);
+  const long long groups = (long long)a->B * a->Sq * a->Hq;   // 8 lanes each, 32 groups per block
+  int dgrid = (int)((groups + 31) / 32);
   if (dgrid > sm_count() * 16) dgrid = sm_count() * 16;
   attn_delta_kernel<<<dgrid, 256, 0, st>>>((const __nv_bfloat16*)a->o, a->ldo, (const __nv_bfloat16*)a->dout, a->lddo,
                                           a->delta, a->B, a->Sq, a->Hq, kBwdHD);

@@ -122,23 +122,41 @@ unary_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restric
 }
 
 // Column sums of a [rows, cols] matrix with leading dimension ld: stage 1 writes [gridDim.y, cols] partials.
+// A block covers 64 columns (32 lanes x 2 adjacent columns) x 8 row lanes; gridDim.x tiles columns, gridDim.y rows.
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const T* __restrict__ x, long long ld, long long rows, int cols, float* __restrict__ partial) {
-  // block = 32 columns x 8 row lanes; gridDim.x tiles columns, gridDim.y tiles rows.
-  __shared__ float sm[8][33];
+  __shared__ float sm[8][65];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + cx;
-  float s = 0.0f;
-  if (c < cols)
-    for (long long r = (long long)blockIdx.y * 8 + ry; r < rows; r += (long long)gridDim.y * 8) s += to_f32(x[r * ld + c]);
-  sm[ry][cx] = s;
+  const int c = blockIdx.x * 64 + cx * 2;
+  float s0 = 0.0f, s1 = 0.0f;
+  const bool pair_ok = (c + 1 < cols) && ((ld & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 3) == 0 || sizeof(T) == 4);
+  if (c < cols) {
+    const long long step = (long long)gridDim.y * 8;
+#pragma unroll 4
+    for (long long r = (long long)blockIdx.y * 8 + ry; r < rows; r += step) {
+      if (pair_ok && sizeof(T) == 2) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(
+            reinterpret_cast<const __nv_bfloat16*>(x) + r * ld + c));
+        s0 += v.x;
+        s1 += v.y;
+      } else {
+        s0 += to_f32(x[r * ld + c]);
+        if (c + 1 < cols) s1 += to_f32(x[r * ld + c + 1]);
+      }
+    }
+  }
+  sm[ry][cx * 2] = s0;
+  sm[ry][cx * 2 + 1] = s1;
   __syncthreads();
-  if (ry == 0 && c < cols) {
-    float t = 0.0f;
+  if (threadIdx.x < 64) {
+    const int cc = blockIdx.x * 64 + threadIdx.x;
+    if (cc < cols) {
+      float t = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) t += sm[k][cx];
-    partial[(long long)blockIdx.y * cols + c] = t;
+      for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+      partial[(long long)blockIdx.y * cols + cc] = t;
+    }
   }
 }
 template <typename T>
@@ -147,6 +165,7 @@ colsum_final_kernel(const float* __restrict__ partial, int nparts, int cols, T* 
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   float s = 0.0f;
+#pragma unroll 8
   for (int p = 0; p < nparts; ++p) s += partial[(long long)p * cols + c];
   if (accumulate) s += to_f32(out[c]);
   out[c] = from_f32<T>(s);
@@ -461,7 +480,7 @@ extern "C" int dptb_colsum(const void* x, long long ld, void* out, float* partia
   if (cols <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
   if (nparts < 1) return kErrBadShape;
-  dim3 grid((cols + 31) / 32, nparts);
+  dim3 grid((cols + 63) / 64, nparts);
   DPTB_BY_DTYPE(dtype,
                 (colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, rows, cols, partial)),
                 (colsum_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ld, rows, cols, partial)));

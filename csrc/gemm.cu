@@ -184,16 +184,210 @@ __device__ __forceinline__ void epilogue_vec32(const GemmParams& p, long long ro
   }
 }
 
+// Activation (or activation-derivative multiply) on 8 values, dispatched once per group so the loops stay branch-free.
+__device__ __forceinline__ void apply_act8(int act, float (&v)[8]) {
+  switch (act) {
+    case 1:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = fmaxf(v[i], 0.0f);
+      break;
+    case 2:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float x = v[i];
+        v[i] = 0.5f * x * (1.0f + tanh_fast(0.7978845608028654f * fmaf(0.044715f * x * x, x, x)));
+      }
+      break;
+    case 3:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-1.702f * v[i]));
+      break;
+    case 4:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i]));
+      break;
+    default: break;
+  }
+}
+__device__ __forceinline__ void apply_act_bwd8(int act, float (&v)[8], const float (&x)[8]) {
+  switch (act) {
+    case 11:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = x[i] > 0.0f ? v[i] : 0.0f;
+      break;
+    case 12:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xx = x[i] * x[i];
+        const float t = tanh_fast(0.7978845608028654f * fmaf(0.044715f * xx, x[i], x[i]));
+        const float d = 0.5f * (1.0f + t) + 0.5f * x[i] * (1.0f - t * t) * (0.7978845608028654f + 0.1070322243f * xx);
+        v[i] *= d;
+      }
+      break;
+    case 13:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float sg = __fdividef(1.0f, 1.0f + __expf(-1.702f * x[i]));
+        v[i] *= sg + 1.702f * x[i] * sg * (1.0f - sg);
+      }
+      break;
+    case 14:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float sg = __fdividef(1.0f, 1.0f + __expf(-x[i]));
+        v[i] *= sg * (1.0f + x[i] * (1.0f - sg));
+      }
+      break;
+    default: break;
+  }
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  return u;
+}
+
+// Second phase of the staged epilogue.  `stage` holds a 32-row x 64-column bf16 block of alpha-scaled accumulators (rows
+// 128 bytes, 16-byte chunks XOR-swizzled by row).  Lanes are re-mapped so that 8 lanes cover one row's 128 bytes:
+// every global access of the warp is 4 full 128-byte row segments.  bias -> aux_out -> act -> act' -> residual -> (+C) -> C.
+__device__ __forceinline__ void epilogue_phase2(const GemmParams& p, const uint8_t* stage, long long row0, long long col0,
+                                                int lane) {
+  const int rg = lane >> 3, cg = lane & 7;
+  const long long col = col0 + cg * 8;
+  const bool full = p.vec_ok && (col0 + 64 <= p.N);
+  float bias8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (p.bias) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (col + e < p.N)
+        bias8[e] = p.bias_f32 ? __ldg(static_cast<const float*>(p.bias) + col + e)
+                              : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + e]);
+  }
+  __nv_bfloat16* C = static_cast<__nv_bfloat16*>(p.C);
+#pragma unroll 2
+  for (int it = 0; it < 8; ++it) {
+    const int rl = it * 4 + rg;
+    const long long row = row0 + rl;
+    if (row >= p.M) continue;
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((cg ^ (rl & 7)) << 4));
+    float v[8];
+    unpack8(raw, v);
+    if (p.bias) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += bias8[e];
+    }
+    if (full) {
+      if (p.aux_out) *reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col) = pack8(v);
+      if (p.act >= 1 && p.act <= 4) apply_act8(p.act, v);
+      if (p.act >= 11) {
+        float x[8];
+        unpack8(*reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col), x);
+        apply_act_bwd8(p.act, v, x);
+      }
+      if (p.residual) {
+        float r[8];
+        unpack8(*reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col), r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += r[e];
+      }
+      if (p.accumulate) {
+        float o[8];
+        unpack8(*reinterpret_cast<const uint4*>(C + row * p.ldc + col), o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += o[e];
+      }
+      *reinterpret_cast<uint4*>(C + row * p.ldc + col) = pack8(v);
+    } else {
+      float x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (col + e < p.N) {
+          if (p.aux_out) p.aux_out[row * p.ld_aux_out + col + e] = __float2bfloat16(v[e]);
+          if (p.act >= 11) x[e] = __bfloat162float(p.aux_in[row * p.ld_aux_in + col + e]);
+        }
+      if (p.act >= 1 && p.act <= 4) apply_act8(p.act, v);
+      if (p.act >= 11) apply_act_bwd8(p.act, v, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (col + e < p.N) {
+          float o = v[e];
+          if (p.residual) o += __bfloat162float(p.residual[row * p.ldr + col + e]);
+          if (p.accumulate) o += __bfloat162float(C[row * p.ldc + col + e]);
+          C[row * p.ldc + col + e] = __float2bfloat16(o);
+        }
+    }
+  }
+}
+
+// fp32-output epilogue for 32 consecutive columns of one row straight from registers (row-per-thread mapping).
+__device__ __forceinline__ void epilogue_direct_f32(const GemmParams& p, long long row, long long col,
+                                                    const uint32_t (&r)[32]) {
+  const bool full = p.vec_ok && (col + 32 <= p.N);
+  float* C = static_cast<float*>(p.C) + row * p.ldc + col;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float v[8], x[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[e] = __uint_as_float(r[g * 8 + e]) * p.alpha;
+      const long long c = col + g * 8 + e;
+      if (c < p.N) {
+        if (p.bias) v[e] += p.bias_f32 ? __ldg(static_cast<const float*>(p.bias) + c)
+                                       : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[c]);
+        if (p.aux_out) p.aux_out[row * p.ld_aux_out + c] = __float2bfloat16(v[e]);
+        if (p.act >= 11) x[e] = __bfloat162float(p.aux_in[row * p.ld_aux_in + c]);
+      }
+    }
+    if (p.act >= 1 && p.act <= 4) apply_act8(p.act, v);
+    if (p.act >= 11) apply_act_bwd8(p.act, v, x);
+    if (full) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float4 o = make_float4(v[h * 4], v[h * 4 + 1], v[h * 4 + 2], v[h * 4 + 3]);
+        if (p.residual) {
+          const __nv_bfloat16* rr = p.residual + row * p.ldr + col + g * 8 + h * 4;
+          o.x += __bfloat162float(rr[0]); o.y += __bfloat162float(rr[1]);
+          o.z += __bfloat162float(rr[2]); o.w += __bfloat162float(rr[3]);
+        }
+        float4* dst = reinterpret_cast<float4*>(C + g * 8 + h * 4);
+        if (p.accumulate) {
+          const float4 c4 = *dst;
+          o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
+        }
+        *dst = o;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const long long c = col + g * 8 + e;
+        if (c < p.N) {
+          float o = v[e];
+          if (p.residual) o += __bfloat162float(p.residual[row * p.ldr + c]);
+          if (p.accumulate) o += C[g * 8 + e];
+          C[g * 8 + e] = o;
+        }
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- tensor-core kernel
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
 
 template <int BN, int STAGES>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kBarOffset = STAGES * (kABytes + kBBytes);
+  static constexpr int kStageOff = STAGES * (kABytes + kBBytes);   // epilogue staging: 4 KB per epilogue warp
+  static constexpr int kBarOffset = kStageOff + kEpiWarps * 4096;
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1) * 8 + 16 + 1024;  // + alignment slack
 };
 
@@ -231,7 +425,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       for (int a = 0; a < 2; ++a) {
         mbar_init(&tmem_full[a], 1);
-        mbar_init(&tmem_empty[a], 4);
+        mbar_init(&tmem_empty[a], kEpiWarps);
       }
       mbar_init(drain_bar, 1);
       mbar_fence_init();
@@ -332,8 +526,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue warps
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue warps (two per TMEM lane quarter)
+    const int ew = warp - 2;
+    const int q = warp & 3;      // TMEM lane quarter this warp may read
+    const int half = ew >> 2;    // takes the 64-column chunks with this parity
+    uint8_t* stage = smem + L::kStageOff + ew * 4096;
     uint32_t local_tile = 0;
     for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
       const int m0 = (tile % p.tiles_m) * kBM;
@@ -342,25 +539,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout))) break;
       tc_fence_after_sync();
-      const long long row = (long long)m0 + q * 32 + lane;
+      const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const long long col = (long long)n0 + c * 32;
-        if (col >= p.N) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
+      for (int c = half; c < BN / 64; c += 2) {
+        const long long col0 = (long long)n0 + c * 64;
+        if (col0 >= p.N) break;  // warp-uniform
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(t_row + c * 64, r0);
+        tmem_ld_32x32(t_row + c * 64 + 32, r1);
         tmem_ld_wait();
-        if (row < p.M) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.vec_ok && col + 32 <= p.N) {
-            epilogue_vec32(p, row, col, v);
-          } else {
-            for (int i = 0; i < 32; ++i)
-              if (col + i < p.N) epilogue_scalar(p, row, col + i, v[i]);
+        if (p.out_f32) {
+          if (row0 + lane < p.M) {
+            epilogue_direct_f32(p, row0 + lane, col0, r0);
+            if (col0 + 32 < p.N) epilogue_direct_f32(p, row0 + lane, col0 + 32, r1);
           }
+        } else {
+          // Phase 1: this thread's row (64 columns) -> bf16 -> staging block.
+          uint8_t* srow = stage + lane * 128;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t* src = g < 4 ? &r0[g * 8] : &r1[(g - 4) * 8];
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
+            u.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
+            u.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
+            u.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
+            *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = u;
+          }
+          __syncwarp();
+          epilogue_phase2(p, stage, row0, col0, lane);
+          __syncwarp();
         }
       }
       tc_fence_before_sync();

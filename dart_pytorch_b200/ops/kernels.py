@@ -330,7 +330,7 @@ def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bo
     if out is None:
         out = torch.empty(cols, dtype=x2d.dtype, device=x2d.device)
         accumulate = False
-    nparts = max(1, min(256, (rows + 63) // 64))
+    nparts = max(1, min(48, (rows + 255) // 256))
     partial = torch.empty(nparts * cols, dtype=torch.float32, device=x2d.device)
     N.check(lib.dptb_colsum(x2d.data_ptr(), _lead(x2d), out.data_ptr(), partial.data_ptr(), rows, cols, nparts,
                             int(accumulate), N.dtype_code(x2d), N.stream_ptr()), "colsum")
