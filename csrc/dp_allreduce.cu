@@ -1,0 +1,255 @@
+// Data-parallel gradient all-reduce over NVLink / NVSwitch peer memory, fused with the sum-of-squares partials that
+// gradient clipping needs.  No NCCL call: the kernel itself issues multimem (in-switch reduction) or plain peer
+// loads / stores and synchronises ranks through flag words in a symmetric signal buffer.
+//
+// It replaces the reference's only multi-replica mechanism, averaging whole checkpoints on the CPU every K local steps
+// (reference: lib/core/coop/param_avg.dart:20-123), with synchronous intra-node data parallelism.
+//
+// Layout.  Every rank holds the same flat bf16 gradient buffer in symmetric memory; `bases[r]` is rank r's copy mapped
+// into this process, `mc_base` the multicast address of all copies (0 when the fabric has none).  A launch handles one
+// bucket [start, start + n).  Rank r owns the r-th slice of the bucket: it reads that slice from every rank, adds in
+// fp32 in rank order, scales by 1 / world, writes the average back into every rank's copy, and accumulates the sum of
+// squares of what it wrote.
+//
+// Protocol per bucket b (epoch e = launches of this bucket so far, kept in device memory so CUDA graphs can replay):
+//   ready[b][src] = e   written into every peer's signal buffer at kernel start (stream order puts it after the
+//                       backward kernels that produced the bucket)
+//   wait until ready[b][*] >= e locally (bounded), then reduce the owned slice
+//   last CTA of the grid: fold the per-CTA sums in CTA order, publish sumsq[b][rank] and done[b][rank] = e to every peer
+// dp_finalize waits (bounded) for done[*][*] >= e, adds sumsq[*][*] in fixed order and writes the clip control block
+// {norm, scale, finite, sumsq}; the optimizer kernel that follows therefore sees fully reduced gradients.
+// Every wait is bounded; a wait that runs out records kWaitFlagTimeout in the status word and the kernel returns.
+#include <cuda_bf16.h>
+
+#include "common/host.h"
+#include "common/ptx.cuh"
+#include "common/reduce.cuh"
+
+namespace dptb {
+
+constexpr int kMaxRanks = 8;
+constexpr int kDpThreads = 512;
+
+struct DpArgs {
+  __nv_bfloat16* bases[kMaxRanks];   // flat gradient buffer of every rank
+  uint32_t* pads[kMaxRanks];         // signal buffer of every rank
+  __nv_bfloat16* mc_base;            // multicast address of the gradient buffers, or null
+  int rank, world;
+  int bucket, num_buckets;
+  long long start, n;                // element range of this bucket (multiples of 8)
+  float* cta_partial;                // local scratch [gridDim.x]
+  unsigned int* cta_counter;         // local, zero between launches
+  unsigned int* epochs;              // local [num_buckets]
+};
+
+// Signal buffer layout (32-bit words): ready[b][r] | done[b][r] | sumsq[b][r] (float bits)
+__device__ __forceinline__ long long pad_ready(int nb, int b, int r) { return ((long long)b * kMaxRanks + r); }
+__device__ __forceinline__ long long pad_done(int nb, int b, int r) { return ((long long)(nb + b) * kMaxRanks + r); }
+__device__ __forceinline__ long long pad_sumsq(int nb, int b, int r) { return ((long long)(2 * nb + b) * kMaxRanks + r); }
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait for *p >= target.  Returns false (and records the failure) when it gives up.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while ((int32_t)(ld_acquire_sys(p) - target) < 0) {
+    if ((++spins & 0x3f) == 0) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
+        report_error(kWaitFlagTimeout);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_cg_v4(void* p, const uint4& v) {
+  asm volatile("st.global.cg.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+template <bool NVLS>
+__global__ void __launch_bounds__(kDpThreads)
+dp_allreduce_kernel(const DpArgs a) {
+  __shared__ float scratch[33];
+  __shared__ int s_ok;
+  __shared__ unsigned int s_last;
+  const int nb = a.num_buckets, b = a.bucket;
+  uint32_t* my_pad = a.pads[a.rank];
+  const uint32_t e = a.epochs[b] + 1;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < a.world) {
+    // Tell every rank that this rank's gradients of bucket b are final (redundant across CTAs: same value).
+    __threadfence_system();
+    st_release_sys(a.pads[threadIdx.x] + pad_ready(nb, b, a.rank), e);
+    if (!wait_flag_ge(my_pad + pad_ready(nb, b, threadIdx.x), e)) s_ok = 0;
+  }
+  __syncthreads();
+  float sq = 0.0f;
+  if (s_ok) {
+    // Slice owned by this rank, in 8-element (16-byte) vectors.
+    const long long nvec = a.n / 8;
+    const long long per = (nvec + a.world - 1) / a.world;
+    const long long v0 = per * a.rank;
+    const long long v1 = v0 + per < nvec ? v0 + per : nvec;
+    const float inv = 1.0f / (float)a.world;
+    for (long long v = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v1;
+         v += (long long)gridDim.x * blockDim.x) {
+      const long long off = a.start + v * 8;
+      float f[8];
+      if (NVLS) {
+        const uint4 u = multimem_ld_reduce_bf16x8(a.mc_base + off);
+        const float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y), p2 = unpack_bf16x2(u.z), p3 = unpack_bf16x2(u.w);
+        f[0] = p0.x; f[1] = p0.y; f[2] = p1.x; f[3] = p1.y; f[4] = p2.x; f[5] = p2.y; f[6] = p3.x; f[7] = p3.y;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.0f;
+        for (int r = 0; r < a.world; ++r) {
+          const uint4 u = ld_cg_v4(a.bases[r] + off);
+          const float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y), p2 = unpack_bf16x2(u.z), p3 = unpack_bf16x2(u.w);
+          f[0] += p0.x; f[1] += p0.y; f[2] += p1.x; f[3] += p1.y; f[4] += p2.x; f[5] += p2.y; f[6] += p3.x; f[7] += p3.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(f[0] * inv, f[1] * inv);
+      o.y = pack_bf16x2(f[2] * inv, f[3] * inv);
+      o.z = pack_bf16x2(f[4] * inv, f[5] * inv);
+      o.w = pack_bf16x2(f[6] * inv, f[7] * inv);
+      // Sum of squares of the values every rank will hold (after bf16 rounding).
+      const float2 q0 = unpack_bf16x2(o.x), q1 = unpack_bf16x2(o.y), q2 = unpack_bf16x2(o.z), q3 = unpack_bf16x2(o.w);
+      sq += q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y + q2.x * q2.x + q2.y * q2.y + q3.x * q3.x + q3.y * q3.y;
+      if (NVLS) {
+        multimem_st_bf16x8(a.mc_base + off, o);
+      } else {
+        for (int r = 0; r < a.world; ++r) st_cg_v4(a.bases[r] + off, o);
+      }
+    }
+  }
+  __threadfence_system();  // this thread's slice writes are visible system-wide before the CTA reports
+  sq = block_sum(sq, scratch);
+  if (threadIdx.x == 0) {
+    a.cta_partial[blockIdx.x] = sq;
+    __threadfence_system();
+    s_last = atomicAdd(a.cta_counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    // Last CTA of this rank: every slice write of this rank has been issued and fenced.
+    __threadfence_system();
+    float tot = 0.0f;
+    if (threadIdx.x == 0) {
+      for (unsigned i = 0; i < gridDim.x; ++i) tot += __ldcg(a.cta_partial + i);
+      *a.cta_counter = 0;
+      a.epochs[b] = e;
+    }
+    tot = __shfl_sync(0xffffffffu, tot, 0);
+    if (threadIdx.x < a.world) {
+      uint32_t* pad = a.pads[threadIdx.x];
+      pad[pad_sumsq(nb, b, a.rank)] = __float_as_uint(tot);
+      __threadfence_system();
+      st_release_sys(pad + pad_done(nb, b, a.rank), e);
+    }
+  }
+}
+
+// One CTA: wait for every (bucket, rank) of this step, fold the sums of squares, write the clip control block.
+__global__ void __launch_bounds__(256)
+dp_finalize_kernel(const uint32_t* pad, const unsigned int* epochs, int num_buckets, int world, float max_norm,
+                   float* ctrl) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const int total = num_buckets * world;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int b = i / world, r = i % world;
+    if (!wait_flag_ge(pad + pad_done(num_buckets, b, r), epochs[b])) s_ok = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.0f;
+    for (int b = 0; b < num_buckets; ++b)
+      for (int r = 0; r < world; ++r) s += __uint_as_float(ld_acquire_sys(pad + pad_sumsq(num_buckets, b, r)));
+    if (!s_ok) s = NAN;
+    const float total_norm = sqrtf(s);
+    const bool finite = isfinite(total_norm);
+    float scale = 1.0f;
+    if (finite && max_norm > 0.0f && total_norm > max_norm) scale = max_norm / total_norm;
+    ctrl[0] = total_norm;
+    ctrl[1] = scale;
+    ctrl[2] = finite ? 1.0f : 0.0f;
+    ctrl[3] = s;
+  }
+}
+
+}  // namespace dptb
+
+using namespace dptb;
+
+struct DptbDpArgs {
+  void* bases[kMaxRanks];
+  void* pads[kMaxRanks];
+  void* mc_base;
+  int rank, world, bucket, num_buckets;
+  long long start, n;
+  float* cta_partial;
+  unsigned int* cta_counter;
+  unsigned int* epochs;
+  int grid;
+  int use_nvls;
+};
+
+// Words a signal buffer needs for `num_buckets` buckets.
+extern "C" long long dptb_dp_pad_words(int num_buckets) { return 3LL * num_buckets * kMaxRanks; }
+
+extern "C" int dptb_dp_allreduce(const DptbDpArgs* h, void* stream) {
+  auto st = static_cast<cudaStream_t>(stream);
+  if (h->world < 1 || h->world > kMaxRanks || h->rank < 0 || h->rank >= h->world) return kErrBadShape;
+  if (h->n <= 0) return 0;
+  if ((h->n % 8) || (h->start % 8) || h->grid < 1) return kErrBadShape;
+  DpArgs a;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    a.bases[r] = static_cast<__nv_bfloat16*>(h->bases[r]);
+    a.pads[r] = static_cast<uint32_t*>(h->pads[r]);
+  }
+  a.mc_base = static_cast<__nv_bfloat16*>(h->mc_base);
+  a.rank = h->rank; a.world = h->world; a.bucket = h->bucket; a.num_buckets = h->num_buckets;
+  a.start = h->start; a.n = h->n;
+  a.cta_partial = h->cta_partial; a.cta_counter = h->cta_counter; a.epochs = h->epochs;
+  if (h->use_nvls && a.mc_base) dp_allreduce_kernel<true><<<h->grid, kDpThreads, 0, st>>>(a);
+  else                          dp_allreduce_kernel<false><<<h->grid, kDpThreads, 0, st>>>(a);
+  return counted(1, (int)cudaGetLastError());
+}
+
+extern "C" int dptb_dp_finalize(const void* pad, const unsigned int* epochs, int num_buckets, int world,
+                                float max_norm, float* ctrl, void* stream) {
+  dp_finalize_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(pad), epochs,
+                                                                     num_buckets, world, max_norm, ctrl);
+  return counted(1, (int)cudaGetLastError());
+}

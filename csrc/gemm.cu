@@ -41,6 +41,12 @@ struct GemmParams {
   float alpha;
   int vec_ok;      // all pointers 16-byte aligned and leading dimensions multiples of 8 elements
   int tiles_m, tiles_n, num_kb;
+  // Split-K: each tile's K range is cut into `splits` work units of kb_per_split k-blocks; partial accumulators go
+  // through `ws` (fp32, [tile][split][BN][128]) and the last unit of a tile to finish (per-tile counter) folds them in
+  // split order, so the result does not depend on arrival order.
+  int splits, kb_per_split;
+  float* ws;
+  int* counters;
 };
 
 // ----------------------------------------------------------------------------- epilogue math
@@ -388,7 +394,7 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageOff = STAGES * (kABytes + kBBytes);   // epilogue staging: 4 KB per epilogue warp
   static constexpr int kBarOffset = kStageOff + kEpiWarps * 4096;
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1) * 8 + 16 + 1024;  // + alignment slack
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1) * 8 + 32 + 1024;  // + alignment slack
 };
 
 template <bool A_MN, bool B_MN, int BN, int STAGES>
@@ -407,13 +413,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* drain_bar = tmem_empty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* epi_ctr = reinterpret_cast<int*>(tmem_slot + 2);       // arrival counter of the epilogue-warp barrier
+  volatile int* epi_last = reinterpret_cast<volatile int*>(tmem_slot + 3);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_units = num_tiles * p.splits;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *epi_ctr = 0;
+    *epi_last = 0;
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
@@ -442,10 +453,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t issued = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x) {
+        const int tile = unit % num_tiles;
+        const int kb0 = (unit / num_tiles) * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         const int m0 = (tile % p.tiles_m) * kBM;
         const int n0 = (tile / p.tiles_m) * BN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++issued) {
+        for (int kb = kb0; kb < kb1; ++kb, ++issued) {
           const int s = issued % STAGES;
           const uint32_t ph = (issued / STAGES) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) break;
@@ -488,14 +502,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t consumed = 0;
       uint32_t local_tile = 0;
       bool issued_any = false;
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
+      for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
+        const int kb0 = (unit / num_tiles) * p.kb_per_split;
+        const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, kWaitTmemEmptyTimeout)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++consumed) {
+        for (int kb = kb0; kb < kb1; ++kb, ++consumed) {
           const int s = consumed % STAGES;
           const uint32_t ph = (consumed / STAGES) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, kWaitFullTimeout)) { ok = false; break; }
@@ -506,7 +522,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t da = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024) : make_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           issued_any = true;
           umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
@@ -532,7 +548,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int half = ew >> 2;    // takes the 64-column chunks with this parity
     uint8_t* stage = smem + L::kStageOff + ew * 4096;
     uint32_t local_tile = 0;
-    for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local_tile) {
+    int epi_gen = 0;
+    // Registers of one 64-column chunk of this thread's row -> final epilogue (staged bf16 path or direct fp32 path).
+    auto emit = [&](long long row0, long long col0, const uint32_t (&r0)[32], const uint32_t (&r1)[32]) {
+      if (p.out_f32) {
+        if (row0 + lane < p.M) {
+          epilogue_direct_f32(p, row0 + lane, col0, r0);
+          if (col0 + 32 < p.N) epilogue_direct_f32(p, row0 + lane, col0 + 32, r1);
+        }
+      } else {
+        uint8_t* srow = stage + lane * 128;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t* src = g < 4 ? &r0[g * 8] : &r1[(g - 4) * 8];
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
+          u.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
+          u.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
+          u.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
+          *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = u;
+        }
+        __syncwarp();
+        epilogue_phase2(p, stage, row0, col0, lane);
+        __syncwarp();
+      }
+    };
+    // Bounded barrier over the epilogue warps (a hardware named barrier could not give up).
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      epi_gen += kEpiWarps;
+      if (lane == 0) {
+        __threadfence_block();
+        atomicAdd(epi_ctr, 1);
+        uint64_t t0 = 0;
+        uint32_t spins = 0;
+        while (*reinterpret_cast<volatile int*>(epi_ctr) < epi_gen) {
+          if ((++spins & 0xff) == 0) {
+            if (*abort_flag) break;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitLimitNs) {
+              *abort_flag = 1;
+              report_error(kWaitFlagTimeout);
+              break;
+            }
+          }
+        }
+        __threadfence_block();
+      }
+      __syncwarp();
+      return !*abort_flag;
+    };
+    for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
+      const int tile = unit % num_tiles;
+      const int split = unit / num_tiles;
       const int m0 = (tile % p.tiles_m) * kBM;
       const int n0 = (tile / p.tiles_m) * BN;
       const uint32_t acc = local_tile & 1;
@@ -541,40 +610,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after_sync();
       const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      if (p.splits == 1) {
 #pragma unroll 1
-      for (int c = half; c < BN / 64; c += 2) {
-        const long long col0 = (long long)n0 + c * 64;
-        if (col0 >= p.N) break;  // warp-uniform
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(t_row + c * 64, r0);
-        tmem_ld_32x32(t_row + c * 64 + 32, r1);
-        tmem_ld_wait();
-        if (p.out_f32) {
-          if (row0 + lane < p.M) {
-            epilogue_direct_f32(p, row0 + lane, col0, r0);
-            if (col0 + 32 < p.N) epilogue_direct_f32(p, row0 + lane, col0 + 32, r1);
-          }
-        } else {
-          // Phase 1: this thread's row (64 columns) -> bf16 -> staging block.
-          uint8_t* srow = stage + lane * 128;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const uint32_t* src = g < 4 ? &r0[g * 8] : &r1[(g - 4) * 8];
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
-            u.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
-            u.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
-            u.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
-            *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = u;
-          }
-          __syncwarp();
-          epilogue_phase2(p, stage, row0, col0, lane);
-          __syncwarp();
+        for (int c = half; c < BN / 64; c += 2) {
+          const long long col0 = (long long)n0 + c * 64;
+          if (col0 >= p.N) break;  // warp-uniform
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+          emit(row0, col0, r0, r1);
         }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      } else {
+        // Partial accumulator -> workspace, column-major inside the tile so that a warp writes 128 contiguous bytes.
+        float* wtile = p.ws + (size_t)tile * p.splits * (BN * kBM);
+        float* wmine = wtile + (size_t)split * (BN * kBM) + q * 32 + lane;
+#pragma unroll 1
+        for (int c = half; c < BN / 64; c += 2) {
+          if ((long long)n0 + c * 64 >= p.N) break;
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            wmine[(c * 64 + i) * kBM] = __uint_as_float(r0[i]);
+            wmine[(c * 64 + 32 + i) * kBM] = __uint_as_float(r1[i]);
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        __threadfence();
+        if (!epi_sync()) break;
+        if (ew == 0 && lane == 0) {
+          const int old = atomicAdd(&p.counters[tile], 1);
+          const int last = old == p.splits - 1;
+          if (last) p.counters[tile] = 0;  // ready for the next launch
+          *epi_last = last;
+        }
+        if (!epi_sync()) break;
+        const bool last = *epi_last != 0;
+        if (last) {
+          __threadfence();
+          const float* wrow = wtile + q * 32 + lane;
+#pragma unroll 1
+          for (int c = half; c < BN / 64; c += 2) {
+            const long long col0 = (long long)n0 + c * 64;
+            if (col0 >= p.N) break;
+            uint32_t r0[32], r1[32];
+            // Split index outermost: the 32 loads of one split are independent and stay in flight together; the
+            // additions still happen in split order for every element.
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              float acc32[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc32[i] = 0.0f;
+              for (int sp = 0; sp < p.splits; ++sp) {
+                const float* src = wrow + (size_t)sp * (BN * kBM) + (size_t)(c * 64 + hh * 32) * kBM;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc32[i] += __ldcg(src + i * kBM);
+              }
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (hh == 0) r0[i] = __float_as_uint(acc32[i]);
+                else r1[i] = __float_as_uint(acc32[i]);
+              }
+            }
+            emit(row0, col0, r0, r1);
+          }
+        }
+        if (!epi_sync()) break;  // epi_last may be rewritten only after every warp has read it
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
     }
   }
 
@@ -635,7 +745,7 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmP
     DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
   return counted(1, (int)cudaGetLastError());
@@ -663,6 +773,11 @@ struct DptbGemmArgs {
   float alpha;
   int force_simt;
   int bn;        // 0 = choose, else 128 or 256
+  int splits;    // split-K factor: 0 = choose, 1 = off
+  void* ws;      // fp32 scratch for split-K partial tiles (may be null: no split-K)
+  long long ws_bytes;
+  int* counters; // zero-initialised per-tile arrival counters (they return to zero after every launch)
+  int num_counters;
 };
 
 extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
@@ -689,6 +804,7 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
 
   if (!tc_ok) {
     p.tiles_m = p.tiles_n = p.num_kb = 0;
+    p.splits = 1; p.kb_per_split = 0; p.ws = nullptr; p.counters = nullptr;
     dim3 grid((unsigned)((a->N + 63) / 64), (unsigned)((a->M + 63) / 64));
     const long long sam = a->trans_a ? 1 : a->lda, sak = a->trans_a ? a->lda : 1;
     const long long sbk = a->trans_b ? 1 : a->ldb, sbn = a->trans_b ? a->ldb : 1;
@@ -703,15 +819,51 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
     return counted(1, (int)cudaGetLastError());
   }
 
-  // Tile width: 256 when that still fills the machine, else 128.
-  int bn = a->bn;
-  if (bn != 128 && bn != 256) {
-    const long long t256 = (long long)((a->M + kBM - 1) / kBM) * ((a->N + 255) / 256);
-    bn = (a->N > 128 && t256 >= sm_count()) ? 256 : 128;
+  // Tile width and split-K factor from a small cost model (unit: the time of one 128x256x64 k-block).
+  //   a CTA runs ceil(units / SMs) units back to back; a unit costs its k-blocks (a 128-wide tile moves as many bytes
+  //   for half the math, so its k-block counts 0.75) plus a fixed prologue/epilogue, plus the partial-tile round
+  //   trip when K is split.
+  const int sms = sm_count();
+  const int num_kb = (a->K + kBK - 1) / kBK;
+  const int tm = (a->M + kBM - 1) / kBM;
+  int bn = a->bn, splits = a->splits;
+  {
+    double best = 1e30;
+    int best_bn = 128, best_sp = 1;
+    for (int cand_bn = 128; cand_bn <= 256; cand_bn += 128) {
+      if (a->bn == 128 || a->bn == 256) { if (cand_bn != a->bn) continue; }
+      if (cand_bn == 256 && a->N <= 128) continue;
+      const int tiles = tm * ((a->N + cand_bn - 1) / cand_bn);
+      for (int sp = 1; sp <= 8; ++sp) {
+        if (a->splits >= 1 && sp != a->splits) continue;
+        if (sp > 1) {
+          if (!a->ws || !a->counters || tiles > a->num_counters) break;
+          if ((long long)tiles * sp * cand_bn * kBM * 4 > a->ws_bytes) break;
+          if (num_kb / sp < 4) break;
+        }
+        const int kbs = (num_kb + sp - 1) / sp;
+        const long long units = (long long)tiles * sp;
+        const double waves = (double)((units + sms - 1) / sms);
+        const double per_kb = cand_bn == 256 ? 1.0 : 0.75;
+        const double fixed = (cand_bn == 256 ? 8.0 : 5.0) + (sp > 1 ? (cand_bn == 256 ? 6.0 + 1.5 * sp : 4.0 + 1.0 * sp) : 0.0);
+        const double cost = waves * (kbs * per_kb + fixed);
+        if (cost < best) { best = cost; best_bn = cand_bn; best_sp = sp; }
+      }
+    }
+    bn = best_bn;
+    splits = best_sp;
   }
-  p.tiles_m = (a->M + kBM - 1) / kBM;
+  p.tiles_m = tm;
   p.tiles_n = (a->N + bn - 1) / bn;
-  p.num_kb = (a->K + kBK - 1) / kBK;
+  p.num_kb = num_kb;
+  p.splits = splits;
+  p.kb_per_split = (num_kb + splits - 1) / splits;
+  if ((long long)(splits - 1) * p.kb_per_split >= num_kb) {  // keep every split non-empty
+    splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    p.splits = splits;
+  }
+  p.ws = static_cast<float*>(a->ws);
+  p.counters = a->counters;
 
   CUtensorMap tmA, tmB;
   int rc;

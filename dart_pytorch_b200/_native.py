@@ -68,7 +68,8 @@ class GemmArgs(ctypes.Structure):
         ("M", c_int), ("N", c_int), ("K", c_int),
         ("trans_a", c_int), ("trans_b", c_int), ("a_f32", c_int), ("b_f32", c_int),
         ("bias_f32", c_int), ("out_f32", c_int), ("accumulate", c_int), ("act", c_int),
-        ("alpha", c_float), ("force_simt", c_int), ("bn", c_int),
+        ("alpha", c_float), ("force_simt", c_int), ("bn", c_int), ("splits", c_int),
+        ("ws", c_void_p), ("ws_bytes", c_ll), ("counters", c_void_p), ("num_counters", c_int),
     ]
 
 

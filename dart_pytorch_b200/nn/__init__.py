@@ -7,3 +7,4 @@ from .transformer import (Activation, TransformerBlock, TransformerEncoder, Tran
                           TransformerDecoder)
 
 causalMask = causal_mask
+from .moe import (Expert, MoEFeedForward, GateFunction, BiasUpdateRule, ExpertActivation, ExpertVariant)

@@ -23,11 +23,28 @@ def _lead(t: torch.Tensor) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.shape[1], t.stride(0))
 
 
+_SPLITK_WS = {}
+SPLITK_WS_BYTES = 64 << 20
+SPLITK_COUNTERS = 4096
+
+
+def splitk_workspace(device: torch.device):
+    """Per-device scratch of the split-K GEMM path: an fp32 partial-tile buffer and zeroed per-tile counters.  Launches
+    on one stream reuse it in order; the counters return to zero at the end of every launch."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _SPLITK_WS.get(key)
+    if ws is None:
+        ws = (torch.empty(SPLITK_WS_BYTES, dtype=torch.uint8, device=device),
+              torch.zeros(SPLITK_COUNTERS, dtype=torch.int32, device=device))
+        _SPLITK_WS[key] = ws
+    return ws
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
          bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
          aux_out: Optional[torch.Tensor] = None, aux_in: Optional[torch.Tensor] = None, act=None,
          act_bwd=None, accumulate: bool = False, alpha: float = 1.0, force_simt: bool = False, bn: int = 0,
-         n_cols: Optional[int] = None) -> torch.Tensor:
+         n_cols: Optional[int] = None, splits: int = 0) -> torch.Tensor:
     """``out[M,N] = epilogue(op(a) @ op(b))``.
 
     ``a`` is stored ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is stored ``[K,N]`` (or ``[N,K]`` with ``trans_b``,
@@ -85,6 +102,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: bool =
     args.alpha = alpha
     args.force_simt = int(force_simt)
     args.bn = bn
+    args.splits = splits
+    if splits != 1 and not force_simt:
+        ws, counters = splitk_workspace(a.device)
+        args.ws, args.ws_bytes = ws.data_ptr(), ws.numel()
+        args.counters, args.num_counters = counters.data_ptr(), counters.numel()
     N.check(lib.dptb_gemm(ctypes.byref(args), N.stream_ptr()), "gemm")
     return out
 

@@ -37,13 +37,25 @@ class GradReducer:
         else:
             self.mode = "nccl"
 
-    def reduce(self) -> None:
-        """Average ``arena.grad`` across ranks (called after backward, before clip)."""
+    def reduce(self, ctrl: Optional[torch.Tensor] = None, max_norm: float = 0.0) -> bool:
+        """Average ``arena.grad`` across ranks (called after backward, before the optimizer).
+
+        In fused mode the same kernels also produce the global gradient norm: when ``ctrl`` is given it receives
+        {norm, clip scale for ``max_norm``, finite flag, sum of squares} and the method returns True, meaning no
+        separate norm pass is needed.  In NCCL mode it returns False."""
         if self.world == 1:
-            return
+            return False
         if self.impl is not None:
             self.impl.reduce()
-            return
+            if ctrl is None:
+                if not hasattr(self, "_ctrl"):
+                    self._ctrl = torch.zeros(4, dtype=torch.float32, device=self.arena.device)
+                ctrl = self._ctrl
+                self.impl.finalize(ctrl, 0.0)
+                return False
+            self.impl.finalize(ctrl, max_norm)
+            return True
         g = self.arena.grad
         for (s, e) in self.buckets:
             dist.all_reduce(g[s:e], op=dist.ReduceOp.AVG, group=self.group)
+        return False

@@ -41,10 +41,16 @@ class Trainer:
         self.opt.zero_grad()
         loss = self.loss_fn(self.model, x, y)
         loss.backward()
-        if self.reducer is not None:
-            self.reducer.reduce()
         norm = None
-        if self.clip_norm is not None:
+        clipped = False
+        if self.reducer is not None:
+            has_ctrl = self.clip_norm is not None and getattr(self.opt, "arena", None) is not None
+            clipped = self.reducer.reduce(self.opt.ctrl if has_ctrl else None, self.clip_norm or 0.0)
+            if clipped:
+                from ..optim.grad_utils import LazyScalar
+                self.opt.clip_pending = True
+                norm = LazyScalar(self.opt.ctrl, 0)
+        if self.clip_norm is not None and not clipped:
             norm = clip_grad_norm(self.opt, self.clip_norm)
         if split_optimizer:
             self.opt.launch_step()

@@ -199,3 +199,24 @@ def test_grad_norm_and_adam(gdtype):
     assert _rel_err(p, pr) < 1e-4
     assert _rel_err(shadow, pr) < 1e-2
     assert _rel_err(m, mr) < 1e-4 and _rel_err(v, vr) < 1e-4
+
+
+@pytest.mark.parametrize("M,N,Kd,trans_a,trans_b", [(768, 768, 4096, True, False), (384, 520, 2048, True, False),
+                                                    (256, 256, 1024, False, True), (130, 200, 1536, False, False)])
+@pytest.mark.parametrize("splits,bn", [(2, 256), (4, 128), (3, 256), (0, 0)])
+def test_gemm_split_k_matches_and_is_deterministic(M, N, Kd, trans_a, trans_b, splits, bn):
+    a = _mk((Kd, M) if trans_a else (M, Kd), seed=21)
+    b = _mk((N, Kd) if trans_b else (Kd, N), seed=22)
+    bias = _mk((N,), dtype=torch.float32, seed=23)
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        K.gemm(a, b, out, trans_a=trans_a, trans_b=trans_b, bias=bias, splits=splits, bn=bn)
+        outs.append(out)
+    af = a.float().t() if trans_a else a.float()
+    bf = b.float().t() if trans_b else b.float()
+    assert _rel_err(outs[0], af @ bf + bias) < 1e-2
+    assert torch.equal(outs[0], outs[1])
+    acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
+    K.gemm(a, b, acc, trans_a=trans_a, trans_b=trans_b, accumulate=True, splits=splits, bn=bn)
+    assert _rel_err(acc, af @ bf + 1.0) < 1e-2
