@@ -1,0 +1,3 @@
+"""Tokenizers and datasets (reference: lib/core/data/*.dart)."""
+from .tokenizers import CharTokenizer, BpeTokenizer
+from .datasets import (Dataset, ListDataset, DataLoader, LmSample, TextTokenDataset, CsvSample, CsvDataset)
