@@ -209,7 +209,9 @@ def run_ours(args):
             "config": {"model": "gpt2-124m", "global_batch": args.batch * world, "seq_len": SEQ,
                        "parallelism": f"dp{world}", "optimizer": "adamw lr6e-4 wd0.1 clip1.0 warmup-cosine",
                        "cache_policy": "per-step working set (>2 GB of activations and logits) exceeds the 126 MB L2",
-                       "cuda_graph": trainer._graph is not None},
+                       "cuda_graph": trainer._graph is not None,
+                       "grad_reduce": "none" if reducer is None else
+                       (reducer.mode + ("+multimem" if getattr(reducer.impl, "use_nvls", False) else ""))},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": int(hx[0].numel() * 8 + hy[0].numel() * 8), "d2h_bytes_per_step": 4},
