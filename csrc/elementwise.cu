@@ -159,6 +159,72 @@ colsum_partial_kernel(const T* __restrict__ x, long long ld, long long rows, int
     }
   }
 }
+// 16-byte variant for bf16 with cols and ld multiples of 8: a warp covers 256 columns of one row per load, the 8 warps
+// of the block take rows round-robin, 4 loads in flight per thread.
+__global__ void __launch_bounds__(256)
+colsum_partial_vec8_kernel(const __nv_bfloat16* __restrict__ x, long long ld, long long rows, int cols,
+                           float* __restrict__ partial) {
+  __shared__ float sm[8][257];
+  const int lane = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 256 + lane * 8;
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = 0.0f;
+  if (c < cols) {
+    const long long step = (long long)gridDim.y * 8;
+    long long r = (long long)blockIdx.y * 8 + ry;
+    for (; r + 3 * step < rows; r += 4 * step) {
+      Raw8<__nv_bfloat16> v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u].load(x + (r + u * step) * ld + c);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        v[u].unpack(f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j] += f[j];
+      }
+    }
+    for (; r < rows; r += step) {
+      float f[8];
+      Vec8<__nv_bfloat16>::load(x + r * ld + c, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[ry][lane * 8 + j] = s[j];
+  __syncthreads();
+  const int cc = blockIdx.x * 256 + threadIdx.x;
+  if (cc < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][threadIdx.x];
+    partial[(long long)blockIdx.y * cols + cc] = t;
+  }
+}
+// Stage 2 for many partials: a block owns 32 columns, its 8 warps take partials round-robin, fixed-order fold.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_final_wide_kernel(const float* __restrict__ partial, int nparts, int cols, T* __restrict__ out, int accumulate) {
+  __shared__ float sm[8][33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float s = 0.0f;
+  if (c < cols) {
+#pragma unroll 4
+    for (int p = w; p < nparts; p += 8) s += partial[(long long)p * cols + c];
+  }
+  sm[w][lane] = s;
+  __syncthreads();
+  if (w == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += sm[k][lane];
+    if (accumulate) t += to_f32(out[c]);
+    out[c] = from_f32<T>(t);
+  }
+}
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_final_kernel(const float* __restrict__ partial, int nparts, int cols, T* __restrict__ out, int accumulate) {
@@ -480,6 +546,13 @@ extern "C" int dptb_colsum(const void* x, long long ld, void* out, float* partia
   if (cols <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
   if (nparts < 1) return kErrBadShape;
+  if (dtype == 1 && (cols & 7) == 0 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    dim3 vgrid((cols + 255) / 256, nparts);
+    colsum_partial_vec8_kernel<<<vgrid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, rows, cols, partial);
+    DPTB_CUDA_OK(cudaGetLastError());
+    colsum_final_wide_kernel<__nv_bfloat16><<<(cols + 31) / 32, 256, 0, st>>>(partial, nparts, cols, (__nv_bfloat16*)out, accumulate);
+    return counted(2, (int)cudaGetLastError());
+  }
   dim3 grid((cols + 63) / 64, nparts);
   DPTB_BY_DTYPE(dtype,
                 (colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, rows, cols, partial)),

@@ -21,7 +21,7 @@ __device__ __forceinline__ float group_sum(float v, float* scratch) {
 
 // G threads cooperate on one row; a block of 256 threads handles 256 / G rows per iteration.
 template <typename T, int G, int V, bool RMS>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, 3)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                 float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows, int D, float eps) {
   __shared__ float scratch[33];
@@ -127,7 +127,7 @@ norm_fwd_generic_kernel(const T* __restrict__ x, const T* __restrict__ gamma, co
 
 // Backward.  partial: [gridDim.x, 2, D] fp32 (dGamma partials then dBeta partials; RMS uses only the first).
 template <typename T, int G, int V, bool RMS>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, 2)
 norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ gamma,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in, const T* __restrict__ dres,
                 T* __restrict__ dx, float* __restrict__ partial, long long rows, int D) {
@@ -147,24 +147,35 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __re
     const bool live = r < rows;
     const float mean = (live && !RMS) ? mean_in[r] : 0.0f;
     const float rstd = live ? rstd_in[r] : 0.0f;
-    float xh[V][8], gy[V][8];
+    // All loads of the row are issued up front and kept packed; values are unpacked (and x-hat recomputed) in both
+    // passes, which costs a few FMAs and saves the registers that would cap occupancy.
+    Raw8<T> xr[V], dr[V], rr[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int vi = t + i * G;
+      if (live && vi < nvec) {
+        xr[i].load(x + r * D + vi * 8);
+        dr[i].load(dy + r * D + vi * 8);
+        if (dres) rr[i].load(dres + r * D + vi * 8);
+      }
+    }
     float c1 = 0.0f, c2 = 0.0f;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const int vi = t + i * G;
       if (live && vi < nvec) {
         float xv[8], dv[8], gm[8];
-        Vec8<T>::load(x + r * D + vi * 8, xv);
-        Vec8<T>::load(dy + r * D + vi * 8, dv);
+        xr[i].unpack(xv);
+        dr[i].unpack(dv);
         Vec8<T>::load(gamma + vi * 8, gm);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xv[j] - mean) * rstd;
-          gy[i][j] = dv[j] * gm[j];
-          dg_acc[i][j] += dv[j] * xh[i][j];
+          const float xh = (xv[j] - mean) * rstd;
+          const float gy = dv[j] * gm[j];
+          dg_acc[i][j] += dv[j] * xh;
           db_acc[i][j] += dv[j];
-          c1 += gy[i][j];
-          c2 += gy[i][j] * xh[i][j];
+          c1 += gy;
+          c2 += gy * xh;
         }
       }
     }
@@ -174,11 +185,16 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __re
     for (int i = 0; i < V; ++i) {
       const int vi = t + i * G;
       if (live && vi < nvec) {
-        float o[8];
-        if (dres) Vec8<T>::load(dres + r * D + vi * 8, o);
+        float xv[8], dv[8], gm[8], o[8];
+        xr[i].unpack(xv);
+        dr[i].unpack(dv);
+        Vec8<T>::load(gamma + vi * 8, gm);
+        if (dres) rr[i].unpack(o);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float d = RMS ? rstd * (gy[i][j] - xh[i][j] * c2) : rstd * (gy[i][j] - c1 - xh[i][j] * c2);
+          const float xh = (xv[j] - mean) * rstd;
+          const float gy = dv[j] * gm[j];
+          const float d = RMS ? rstd * (gy - xh * c2) : rstd * (gy - c1 - xh * c2);
           o[j] = dres ? o[j] + d : d;
         }
         Vec8<T>::store(dx + r * D + vi * 8, o);

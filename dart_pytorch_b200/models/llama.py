@@ -97,9 +97,9 @@ class Llama(Module):
     def head_weight(self):
         return self.embed_in.weight if self.untied_head is None else self.untied_head.weight
 
-    def forward_from_embeddings(self, h, start_pos: int = 0, cache: Optional[EncoderCache] = None):
-        """Run the decoder stack on precomputed input embeddings ``[N, D]`` / ``[B, N, D]`` (multimodal prefixes);
-        returns final-norm hidden states (reference: lib/core/nn/llama.dart:217-236)."""
+    def hidden_from_embeddings(self, h, start_pos: int = 0, cache: Optional[EncoderCache] = None):
+        """Run the decoder stack on precomputed input embeddings ``[N, D]`` / ``[B, N, D]``; returns the final-norm
+        hidden states."""
         n = h.shape[-2]
         if start_pos + n > self.config.max_ctx:
             raise ValueError(f"Llama: sequence of {start_pos + n} tokens exceeds maxCtx {self.config.max_ctx}")
@@ -109,12 +109,19 @@ class Llama(Module):
             h = blk(h, cache=None if cache is None else cache.layers[i], start_pos=start_pos, causal=n > 1)
         return self.final_norm(h)
 
+    def forward_from_embeddings(self, h, start_pos: int = 0, cache: Optional[EncoderCache] = None):
+        """Logits for precomputed input embeddings (multimodal prefixes mixed with text embeddings): block stack,
+        final norm and output head, skipping the token embedding (reference: lib/core/nn/llama.dart:217-236)."""
+        if h.dim() not in (2, 3) or h.shape[-1] != self.config.embed_dim:
+            raise ValueError(f"Llama.forwardFromEmbeddings: expected [N, {self.config.embed_dim}]; got {list(h.shape)}")
+        return F.linear(self.hidden_from_embeddings(h, start_pos, cache), self.head_weight)
+
     forwardFromEmbeddings = forward_from_embeddings
 
     def hidden(self, tokens, start_pos: int = 0, cache: Optional[EncoderCache] = None):
         if tokens.dim() not in (1, 2):
             raise ValueError("Llama: tokens must be [N] or [B, N]")
-        return self.forward_from_embeddings(F.embedding(self.embed_in.weight, tokens), start_pos, cache)
+        return self.hidden_from_embeddings(F.embedding(self.embed_in.weight, tokens), start_pos, cache)
 
     def forward(self, tokens, start_pos: int = 0, cache: Optional[EncoderCache] = None):
         tokens = _as_token_tensor(tokens, self.device)

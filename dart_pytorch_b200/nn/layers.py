@@ -211,6 +211,7 @@ class VisionProjector(Module):
                  dtype=torch.float32):
         super().__init__()
         hidden = hidden or out_dim
+        self.in_dim, self.out_dim, self.hidden_dim = in_dim, out_dim, hidden
         self.up = Linear(in_dim, hidden, device=device, seed=seed, dtype=dtype)
         self.down = Linear(hidden, out_dim, device=device, seed=seed + 1000, dtype=dtype)
 

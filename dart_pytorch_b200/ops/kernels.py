@@ -287,13 +287,27 @@ def scale_by_ctrl(g_flat, ctrl):
 
 def adam_flat(p, shadow, g, m, v, ctrl, lr, beta1, beta2, eps, weight_decay, bc1, bc2, skip_if_nonfinite=False,
               hyper=None):
+    """``p`` is the fp32 master range, ``shadow`` the optional bf16 working copy written alongside."""
     lib = N.load()
+    n = p.numel()
+    if p.dtype != torch.float32 or m.dtype != torch.float32 or v.dtype != torch.float32:
+        raise TypeError("adam_flat: p, m and v must be float32")
+    if shadow is not None and (shadow.dtype != torch.bfloat16 or shadow.numel() != n):
+        raise TypeError("adam_flat: shadow must be bfloat16 with p's length")
+    if g.numel() != n or m.numel() != n or v.numel() != n:
+        raise ValueError("adam_flat: g, m and v must have p's length")
     N.check(lib.dptb_adam_flat(p.data_ptr(), N.ptr(shadow), g.data_ptr(), N.dtype_code(g), m.data_ptr(), v.data_ptr(),
                                p.numel(), N.ptr(ctrl), lr, beta1, beta2, eps, weight_decay, bc1, bc2,
                                int(skip_if_nonfinite), N.ptr(hyper), N.stream_ptr()), "adam_flat")
 
 
 def sgd_flat(p, shadow, g, buf, ctrl, lr, momentum, weight_decay, first_step):
+    if p.dtype != torch.float32 or g.numel() != p.numel():
+        raise TypeError("sgd_flat: p must be float32 and g must have p's length")
+    if shadow is not None and (shadow.dtype != torch.bfloat16 or shadow.numel() != p.numel()):
+        raise TypeError("sgd_flat: shadow must be bfloat16 with p's length")
+    if buf is not None and (buf.dtype != torch.float32 or buf.numel() != p.numel()):
+        raise TypeError("sgd_flat: buf must be float32 with p's length")
     lib = N.load()
     N.check(lib.dptb_sgd_flat(p.data_ptr(), N.ptr(shadow), g.data_ptr(), N.dtype_code(g), N.ptr(buf), p.numel(),
                               N.ptr(ctrl), lr, momentum, weight_decay, int(first_step), N.stream_ptr()), "sgd_flat")
@@ -352,7 +366,11 @@ def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bo
     if out is None:
         out = torch.empty(cols, dtype=x2d.dtype, device=x2d.device)
         accumulate = False
-    nparts = max(1, min(48, (rows + 255) // 256))
+    if x2d.dtype == torch.bfloat16 and cols % 8 == 0:
+        # 16-byte path: about four 256-column CTAs per SM, at least 32 rows each
+        nparts = max(1, min(256, 592 // ((cols + 255) // 256), (rows + 31) // 32))
+    else:
+        nparts = max(1, min(48, (rows + 255) // 256))
     partial = torch.empty(nparts * cols, dtype=torch.float32, device=x2d.device)
     N.check(lib.dptb_colsum(x2d.data_ptr(), _lead(x2d), out.data_ptr(), partial.data_ptr(), rows, cols, nparts,
                             int(accumulate), N.dtype_code(x2d), N.stream_ptr()), "colsum")

@@ -47,10 +47,10 @@ def test_llama_cache_equals_no_cache_and_batch_equals_single():
         assert torch.allclose(m(x)[1], m(x[1]), atol=1e-5)
     with pytest.raises(ValueError):
         m(torch.zeros(49, dtype=torch.long))
-    # forwardFromEmbeddings == hidden() on the embedded tokens
+    # forwardFromEmbeddings == logits of the embedded tokens
     with torch.no_grad():
         e = m.embed_in(x[0])
-        assert torch.allclose(m.forward_from_embeddings(e), m.hidden(x[0]), atol=1e-6)
+        assert torch.allclose(m.forward_from_embeddings(e), m(x[0]), atol=1e-5)
 
 
 def test_llama_overfits_tiny_sequence_and_checkpoint_round_trip():
