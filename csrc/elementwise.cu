@@ -4,6 +4,7 @@
 // lib/native/src/kernels/transpose.cuh, lib/native/src/kernels/matmul.cuh:146-185, lib/native/src/engine.cu:65-88,575-596)
 // with its numerical conventions: sign-preserving clamped division, NaN-free pow, log with an optional epsilon.
 // Reductions are two-stage and ordered, not one atomicAdd per element.
+#include <initializer_list>
 #include "common/host.h"
 #include "common/reduce.cuh"
 
@@ -357,6 +358,55 @@ swiglu_fwd_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ 
     out[r * ldo + c] = from_f32<T>(gv / (1.0f + __expf(-gv)) * uv);
   }
 }
+// 16-byte variants (cols and every leading dimension multiples of 8 elements, 16-byte aligned bases).
+template <typename T>
+__global__ void __launch_bounds__(kEwThreads)
+swiglu_fwd_vec8_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ u, long long ldu,
+                       T* __restrict__ out, long long ldo, long long rows, int cols) {
+  const int cv = cols >> 3;
+  const long long n = rows * cv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cv;
+    const int c = (int)(i - r * cv) << 3;
+    float gv[8], uv[8], o[8];
+    Vec8<T>::load(g + r * ldg + c, gv);
+    Vec8<T>::load(u + r * ldu + c, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = gv[j] / (1.0f + __expf(-gv[j])) * uv[j];
+    Vec8<T>::store(out + r * ldo + c, o);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(kEwThreads)
+swiglu_bwd_vec8_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ u, long long ldu,
+                       const T* __restrict__ dout, long long ldo, T* __restrict__ dg, long long lddg,
+                       T* __restrict__ du, long long lddu, long long rows, int cols) {
+  const int cv = cols >> 3;
+  const long long n = rows * cv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cv;
+    const int c = (int)(i - r * cv) << 3;
+    float gv[8], uv[8], d[8], a[8], b[8];
+    Vec8<T>::load(g + r * ldg + c, gv);
+    Vec8<T>::load(u + r * ldu + c, uv);
+    Vec8<T>::load(dout + r * ldo + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.0f / (1.0f + __expf(-gv[j]));
+      a[j] = d[j] * uv[j] * sg * (1.0f + gv[j] * (1.0f - sg));
+      b[j] = d[j] * gv[j] * sg;
+    }
+    Vec8<T>::store(dg + r * lddg + c, a);
+    Vec8<T>::store(du + r * lddu + c, b);
+  }
+}
+static inline bool vec8_ok(int cols, std::initializer_list<long long> lds, std::initializer_list<const void*> ptrs,
+                           int elem_bytes) {
+  if (cols & 7) return false;
+  for (long long ld : lds) if (ld & 7) return false;
+  for (const void* p : ptrs) if (reinterpret_cast<uintptr_t>(p) & (elem_bytes * 8 - 1)) return false;
+  return true;
+}
 template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
 swiglu_bwd_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ u, long long ldu,
@@ -484,6 +534,56 @@ im2col_nhwc_kernel(const T* __restrict__ in, T* __restrict__ out, int batch, int
     T v = from_f32<T>(0.0f);
     if (y >= 0 && y < board && x >= 0 && x < board) v = in[((long long)b * board * board + y * board + x) * channels + c];
     out[i] = v;
+  }
+}
+
+// General convolution lowering.  x [B, C, H, W] -> cols [B*Ho*Wo, C*Kh*Kw] (column order (c, ky, kx), matching a
+// [Cout, Cin, Kh, Kw] weight flattened to [Cout, Cin*Kh*Kw]); zero padding (reference: lib/core/nn/conv2d.dart:120-180).
+struct ConvGeom {
+  int B, C, H, W, Kh, Kw, stride, pad, Ho, Wo;
+};
+template <typename T>
+__global__ void __launch_bounds__(kEwThreads)
+im2col_nchw_kernel(const T* __restrict__ x, T* __restrict__ cols, ConvGeom g) {
+  const long long row_len = (long long)g.C * g.Kh * g.Kw;
+  const long long n = (long long)g.B * g.Ho * g.Wo * row_len;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / row_len;
+    const int col = (int)(i - row * row_len);
+    const int kx = col % g.Kw, ky = (col / g.Kw) % g.Kh, c = col / (g.Kw * g.Kh);
+    const int wo = (int)(row % g.Wo), ho = (int)((row / g.Wo) % g.Ho), b = (int)(row / ((long long)g.Wo * g.Ho));
+    const int y = ho * g.stride - g.pad + ky, xx = wo * g.stride - g.pad + kx;
+    T v = from_f32<T>(0.0f);
+    if (y >= 0 && y < g.H && xx >= 0 && xx < g.W) v = x[(((long long)b * g.C + c) * g.H + y) * g.W + xx];
+    cols[i] = v;
+  }
+}
+// Adjoint of the lowering: dx[b, c, y, x] = sum over the (ky, kx, ho, wo) that read it.  Gather form, so no atomics and
+// a fixed summation order.
+template <typename T>
+__global__ void __launch_bounds__(kEwThreads)
+col2im_nchw_kernel(const T* __restrict__ cols, T* __restrict__ dx, ConvGeom g) {
+  const long long row_len = (long long)g.C * g.Kh * g.Kw;
+  const long long n = (long long)g.B * g.C * g.H * g.W;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int xx = (int)(i % g.W), y = (int)((i / g.W) % g.H);
+    const int c = (int)((i / ((long long)g.W * g.H)) % g.C), b = (int)(i / ((long long)g.W * g.H * g.C));
+    float acc = 0.0f;
+    for (int ky = 0; ky < g.Kh; ++ky) {
+      const int yy = y + g.pad - ky;
+      if (yy < 0 || yy % g.stride) continue;
+      const int ho = yy / g.stride;
+      if (ho >= g.Ho) continue;
+      for (int kx = 0; kx < g.Kw; ++kx) {
+        const int xw = xx + g.pad - kx;
+        if (xw < 0 || xw % g.stride) continue;
+        const int wo = xw / g.stride;
+        if (wo >= g.Wo) continue;
+        const long long row = ((long long)b * g.Ho + ho) * g.Wo + wo;
+        acc += to_f32(cols[row * row_len + ((long long)c * g.Kh + ky) * g.Kw + kx]);
+      }
+    }
+    dx[i] = from_f32<T>(acc);
   }
 }
 
@@ -624,6 +724,13 @@ extern "C" int dptb_swiglu_fwd(const void* g, long long ldg, const void* u, long
                                long long rows, int cols, int dtype, void* stream) {
   if (rows <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
+  if (vec8_ok(cols, {ldg, ldu, ldo}, {g, u, out}, dtype ? 2 : 4)) {
+    const long long nv = rows * (cols >> 3);
+    DPTB_BY_DTYPE(dtype,
+                  (swiglu_fwd_vec8_kernel<__nv_bfloat16><<<ew_grid(nv), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)out, ldo, rows, cols)),
+                  (swiglu_fwd_vec8_kernel<float><<<ew_grid(nv), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (float*)out, ldo, rows, cols)));
+    return counted(1, (int)cudaGetLastError());
+  }
   DPTB_BY_DTYPE(dtype,
                 (swiglu_fwd_kernel<__nv_bfloat16><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)out, ldo, rows, cols)),
                 (swiglu_fwd_kernel<float><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (float*)out, ldo, rows, cols)));
@@ -634,6 +741,13 @@ extern "C" int dptb_swiglu_bwd(const void* g, long long ldg, const void* u, long
                                int cols, int dtype, void* stream) {
   if (rows <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
+  if (vec8_ok(cols, {ldg, ldu, ldo, lddg, lddu}, {g, u, dout, dg, du}, dtype ? 2 : 4)) {
+    const long long nv = rows * (cols >> 3);
+    DPTB_BY_DTYPE(dtype,
+                  (swiglu_bwd_vec8_kernel<__nv_bfloat16><<<ew_grid(nv), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)dout, ldo, (__nv_bfloat16*)dg, lddg, (__nv_bfloat16*)du, lddu, rows, cols)),
+                  (swiglu_bwd_vec8_kernel<float><<<ew_grid(nv), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (const float*)dout, ldo, (float*)dg, lddg, (float*)du, lddu, rows, cols)));
+    return counted(1, (int)cudaGetLastError());
+  }
   DPTB_BY_DTYPE(dtype,
                 (swiglu_bwd_kernel<__nv_bfloat16><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (const __nv_bfloat16*)dout, ldo, (__nv_bfloat16*)dg, lddg, (__nv_bfloat16*)du, lddu, rows, cols)),
                 (swiglu_bwd_kernel<float><<<ew_grid(rows * cols), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (const float*)dout, ldo, (float*)dg, lddg, (float*)du, lddu, rows, cols)));
@@ -670,6 +784,27 @@ extern "C" int dptb_im2col_nhwc(const void* in, void* out, int batch, int channe
   DPTB_BY_DTYPE(dtype,
                 (im2col_nhwc_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, batch, channels, ksize, board)),
                 (im2col_nhwc_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)in, (float*)out, batch, channels, ksize, board)));
+  return counted(1, (int)cudaGetLastError());
+}
+// direction 0: x -> cols (im2col); 1: cols -> dx (col2im, the adjoint).
+extern "C" int dptb_conv_lower(const void* src, void* dst, int B, int C, int H, int W, int Kh, int Kw, int stride,
+                               int pad, int direction, int dtype, void* stream) {
+  auto st = static_cast<cudaStream_t>(stream);
+  if (B <= 0 || C <= 0 || Kh <= 0 || Kw <= 0 || stride <= 0 || pad < 0) return kErrBadShape;
+  const int Ho = (H + 2 * pad - Kh) / stride + 1, Wo = (W + 2 * pad - Kw) / stride + 1;
+  if (H + 2 * pad < Kh || W + 2 * pad < Kw || Ho <= 0 || Wo <= 0) return kErrBadShape;
+  ConvGeom g{B, C, H, W, Kh, Kw, stride, pad, Ho, Wo};
+  if (direction == 0) {
+    const long long n = (long long)B * Ho * Wo * C * Kh * Kw;
+    DPTB_BY_DTYPE(dtype,
+                  (im2col_nchw_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, g)),
+                  (im2col_nchw_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)src, (float*)dst, g)));
+  } else {
+    const long long n = (long long)B * C * H * W;
+    DPTB_BY_DTYPE(dtype,
+                  (col2im_nchw_kernel<__nv_bfloat16><<<ew_grid(n), kEwThreads, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, g)),
+                  (col2im_nchw_kernel<float><<<ew_grid(n), kEwThreads, 0, st>>>((const float*)src, (float*)dst, g)));
+  }
   return counted(1, (int)cudaGetLastError());
 }
 // in_dtype / out_dtype packed as dtype = in + 2*out.

@@ -118,6 +118,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("dptb_argmax_rows", P, L, P, L, I, I, P)
     sig("dptb_topk_sample", P, L, P, P, L, I, I, F, I, I, P)
     sig("dptb_im2col_nhwc", P, P, I, I, I, I, I, P)
+    sig("dptb_conv_lower", P, P, I, I, I, I, I, I, I, I, I, I, P)
     sig("dptb_aft_fwd", P, P, P, P, P, I, I, I, I, I, P)
     sig("dptb_aft_bwd", P, P, P, P, P, P, P, P, P, I, I, I, I, I, P)
     sig("dptb_patchify", P, P, I, I, I, I, I, I, P)

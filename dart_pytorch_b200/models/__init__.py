@@ -14,3 +14,5 @@ from .sentence import (PoolingMode, TokenEncoder, SentenceEncoder, CrossEncoder,
                        SentenceLosses, pool_tokens, poolTokens, l2_normalize_row, l2NormalizeRow)
 from .muzero_lm import (MuZeroLM, MuZeroRepresentation, MuZeroDynamics, MuZeroPrediction, MuZeroUnroll)
 from .vision_language import CLIPVisionConfig, CLIPVisionModel, LlamaVision
+from .lc0 import (Lc0Net, Lc0Reader, Lc0Input, Lc0Weights, Lc0ConvBlock, Lc0SEUnit, Lc0Residual, Lc0Output, START_FEN,
+                  startFen)

@@ -8,3 +8,4 @@ from .transformer import (Activation, TransformerBlock, TransformerEncoder, Tran
 
 causalMask = causal_mask
 from .moe import (Expert, MoEFeedForward, GateFunction, BiasUpdateRule, ExpertActivation, ExpertVariant)
+from .conv import Conv2d, im2col

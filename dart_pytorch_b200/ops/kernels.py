@@ -474,6 +474,33 @@ def im2col_nhwc(x: torch.Tensor, batch: int, channels: int, ksize: int, board: i
     return out
 
 
+def conv_out_size(size: int, k: int, stride: int, pad: int) -> int:
+    return (size + 2 * pad - k) // stride + 1
+
+
+def im2col_nchw(x: torch.Tensor, kh: int, kw: int, stride: int, pad: int) -> torch.Tensor:
+    """``[B, C, H, W]`` -> ``[B*Ho*Wo, C*kh*kw]`` rows, column order ``(c, ky, kx)``, zero padding."""
+    lib = N.load()
+    x = x.contiguous()
+    B, C, H, W = x.shape
+    ho, wo = conv_out_size(H, kh, stride, pad), conv_out_size(W, kw, stride, pad)
+    out = torch.empty(B * ho * wo, C * kh * kw, dtype=x.dtype, device=x.device)
+    N.check(lib.dptb_conv_lower(x.data_ptr(), out.data_ptr(), B, C, H, W, kh, kw, stride, pad, 0, N.dtype_code(x),
+                                N.stream_ptr()), "im2col_nchw")
+    return out
+
+
+def col2im_nchw(cols: torch.Tensor, shape, kh: int, kw: int, stride: int, pad: int) -> torch.Tensor:
+    """Adjoint of :func:`im2col_nchw`: scatter-sums column gradients back to a ``[B, C, H, W]`` image gradient."""
+    lib = N.load()
+    cols = cols.contiguous()
+    B, C, H, W = shape
+    out = torch.empty(B, C, H, W, dtype=cols.dtype, device=cols.device)
+    N.check(lib.dptb_conv_lower(cols.data_ptr(), out.data_ptr(), B, C, H, W, kh, kw, stride, pad, 1,
+                                N.dtype_code(cols), N.stream_ptr()), "col2im_nchw")
+    return out
+
+
 def patchify(img: torch.Tensor, patch: int, out_dtype=None) -> torch.Tensor:
     """``[B, C, H, W]`` image -> ``[B * (H/P) * (W/P), P*P*C]`` rows with per-patch order ``(dy, dx, c)``."""
     lib = N.load()

@@ -1,0 +1,2 @@
+"""Training utilities: flat parameter arena, CUDA-graph trainer, assignment solver."""
+from .hungarian import HungarianAlgorithm
