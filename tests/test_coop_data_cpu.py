@@ -2,6 +2,7 @@
 tokenizers, datasets, safetensors.  Failures are injected on the host: stale rounds, garbled blobs, mismatched headers,
 unreachable peers."""
 import json
+import os
 import random
 import struct
 
@@ -198,3 +199,35 @@ def test_safetensors_dtypes_metadata_shards(tmp_path):
     (tmp_path / "bad.json").write_text("[]")
     with pytest.raises(ValueError):
         SafeTensors.read_shard_index(str(tmp_path / "bad.json"))
+
+
+def test_image_folder_dataset(tmp_path):
+    import numpy as np
+    from PIL import Image
+    from dart_pytorch_b200.data.image_folder import ImageFolderDataset
+    from dart_pytorch_b200.models.vit import patchify
+    rng = np.random.default_rng(0)
+    for cname, n in (("b_cat", 5), ("a_dog", 4), ("c_empty", 0)):
+        os.makedirs(tmp_path / cname)
+        for i in range(n):
+            arr = rng.integers(0, 256, size=(12, 10, 3), dtype=np.uint8)
+            Image.fromarray(arr).save(tmp_path / cname / f"img{i}.png")
+    (tmp_path / "a_dog" / "broken.jpg").write_bytes(b"not an image")
+    (tmp_path / "a_dog" / "notes.txt").write_text("skip me")
+    ds = ImageFolderDataset(str(tmp_path), image_size=8, patch_size=4, val_split=0.25, seed=3)
+    assert ds.classes == ["a_dog", "b_cat"] and ds.num_patches == 4 and ds.patch_pixels == 48
+    assert ds.num_train + ds.num_val == 9 and ds.num_val in (1, 2)   # the unreadable file is skipped wherever it falls
+    s = ds[0]
+    assert s.patches.shape == (4, 48) and 0.0 <= float(s.patches.min()) and float(s.patches.max()) <= 1.0
+    val = ds.val_split()
+    assert len(val) == ds.num_val and val.val_split() is val and len(ds) == ds.num_train
+    # patch order agrees with the model-side patchify of the same image
+    flat = ds._train[0][0]
+    want = patchify(torch.from_numpy(flat).permute(2, 0, 1).unsqueeze(0), 4)[0]
+    assert torch.allclose(ds[0].patches, want)
+    t = ds.sample_triplet()
+    assert t.anchor.shape == (4, 48) and t.anchor_class != t.negative_class
+    with pytest.raises(ValueError):
+        ImageFolderDataset(str(tmp_path), image_size=9, patch_size=4)
+    with pytest.raises(ValueError):
+        ImageFolderDataset(str(tmp_path / "missing"), image_size=8, patch_size=4)
