@@ -34,9 +34,56 @@ class KernelError(RuntimeError):
     """A launcher returned a non-zero code, or a kernel recorded a failure in the device status word."""
 
 
+LIB_NAME = "libdptb200.so"
+
+
+def candidate_paths() -> list:
+    """Discovery order (reference: lib/core/tensor/cuda_engine.dart:428-455): explicit ``DPTB200_NATIVE_LIB``, the working
+    directory, the directory of the running program, then the package's own ``_C`` directory."""
+    import sys
+    out = []
+    env = os.environ.get("DPTB200_NATIVE_LIB")
+    if env:
+        out.append(Path(env))
+    out.append(Path.cwd() / LIB_NAME)
+    if sys.argv and sys.argv[0]:
+        out.append(Path(sys.argv[0]).resolve().parent / LIB_NAME)
+    out.append(_HERE / "_C" / LIB_NAME)
+    return out
+
+
+def looks_like_shared_object(path: Path) -> bool:
+    """ELF magic check, the analogue of the reference's check on a fetched library
+    (lib/core/tensor/native_lib_download.dart:143-162)."""
+    try:
+        with open(path, "rb") as f:
+            return f.read(4) == b"\x7fELF"
+    except OSError:
+        return False
+
+
+def build_native_library() -> Optional[Path]:
+    """Where the reference can fetch a prebuilt library, this build compiles its own: with ``DPTB200_AUTO_BUILD=1`` a
+    missing library is built from ``csrc/`` with ``nvcc`` (when both exist) and its path returned."""
+    import shutil
+    import subprocess
+    import sys
+    script = _HERE.parent / "csrc" / "build.py"
+    if os.environ.get("DPTB200_AUTO_BUILD", "0") != "1" or not script.exists() or shutil.which("nvcc") is None:
+        return None
+    subprocess.run([sys.executable, str(script)], check=True)
+    built = _HERE / "_C" / LIB_NAME
+    return built if looks_like_shared_object(built) else None
+
+
 def lib_path() -> Path:
     env = os.environ.get("DPTB200_NATIVE_LIB")
-    return Path(env) if env else _HERE / "_C" / "libdptb200.so"
+    if env:                      # an explicit override is used as given, even when it does not exist (and then fails)
+        return Path(env)
+    for p in candidate_paths():
+        if p.exists() and looks_like_shared_object(p):
+            return p
+    return build_native_library() or _HERE / "_C" / LIB_NAME
 
 
 def load(required: bool = True) -> Optional[ctypes.CDLL]:

@@ -203,3 +203,20 @@ def test_sampler_greedy_topk_and_seeded():
     a = [F.sample_from_logits(logits, 0.7, None, random.Random(5)) for _ in range(3)]
     b = [F.sample_from_logits(logits, 0.7, None, random.Random(5)) for _ in range(3)]
     assert a == b
+
+
+def test_native_library_discovery_order(tmp_path, monkeypatch):
+    """Env override wins and is taken as given; otherwise cwd, program directory, package directory; non-ELF files
+    are skipped (reference behaviour: native_lib_download_test.dart)."""
+    from dart_pytorch_b200 import _native as N
+    monkeypatch.delenv("DPTB200_NATIVE_LIB", raising=False)
+    monkeypatch.delenv("DPTB200_AUTO_BUILD", raising=False)
+    monkeypatch.chdir(tmp_path)
+    assert N.candidate_paths()[0] == tmp_path / N.LIB_NAME and N.candidate_paths()[-1].parent.name == "_C"
+    (tmp_path / N.LIB_NAME).write_bytes(b"not an elf")
+    assert N.lib_path() != tmp_path / N.LIB_NAME
+    (tmp_path / N.LIB_NAME).write_bytes(b"\x7fELF" + bytes(16))
+    assert N.lib_path() == tmp_path / N.LIB_NAME and N.looks_like_shared_object(tmp_path / N.LIB_NAME)
+    monkeypatch.setenv("DPTB200_NATIVE_LIB", str(tmp_path / "custom.so"))
+    assert N.lib_path() == tmp_path / "custom.so" and N.candidate_paths()[0] == tmp_path / "custom.so"
+    assert N.build_native_library() is None          # opt-in only
