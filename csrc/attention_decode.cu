@@ -1,0 +1,330 @@
+// Decode-time attention over a KV cache (one or a few new query tokens per sequence) and the fused rotary + cache
+// append that precedes it.
+//
+// The reference keeps per-head K / V tensors on the device, re-uploads the whole cache after appending one row on the
+// host and materialises [1, T] score rows per head (reference: lib/core/nn/kv_cache.dart:22-84,
+// lib/core/nn/attention/multi_head_attention.dart:160-235, lib/core/tensor/concat.dart:51-90).  Here the cache is one
+// [B, capacity, Hkv * hd] buffer per layer, new rows are written in place by the kernel that also applies RoPE, and
+// attention streams each KV row exactly once for all query heads that share it (grouped-query attention).
+//
+// attn_decode_kernel: grid (splits, Hkv, B * Sq).  A CTA owns one (sequence, query position, kv head) and a contiguous
+// chunk of the keys; its 4 warps take 32-key blocks round-robin.  Within a warp each lane holds hd/32 dimensions of the
+// current key / value row (one 256-byte coalesced row read per key for hd = 128), scores of the G = Hq / Hkv grouped
+// heads are reduced with shuffles, the softmax is computed per 32-key block (lane j owns key j) and the block's
+// probabilities are broadcast back for the P.V accumulation.  Partial (max, sum, acc) per (warp -> CTA -> split) are
+// merged in shared memory and, when the keys are split across CTAs, through an fp32 workspace by attn_decode_merge.
+// The kernel is memory-bound by design: the roofline is the KV bytes over HBM bandwidth.
+#include <cuda_bf16.h>
+
+#include "common/host.h"
+#include "common/reduce.cuh"
+
+namespace dptb {
+
+constexpr int kDecWarps = 4;
+constexpr int kMaxGroup = 8;   // query heads per kv head
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;    // [B * Sq, ldq], head h at columns [h * hd, (h + 1) * hd)
+  const __nv_bfloat16* k;    // [B, cap, ldkv] rows; kv head g at columns [g * hd, ...)
+  const __nv_bfloat16* v;
+  __nv_bfloat16* o;          // [B * Sq, ldo]
+  float* ws;                 // [B * Sq, Hkv, splits, G, hd + 2] when splits > 1
+  long long ldq, ldkv, ldo;
+  long long kv_batch_stride; // elements between consecutive sequences of the cache (cap * ldkv)
+  int B, Sq, Sk, Hq, Hkv, splits;
+  int q_offset;              // absolute position of query row 0 (causal: query i sees keys <= q_offset + i)
+  float scale;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attn_decode_kernel(const DecodeArgs a) {
+  constexpr int E = HD / 32;                 // dims per lane
+  const int split = blockIdx.x, g = blockIdx.y, bs = blockIdx.z;
+  const int b = bs / a.Sq, sq = bs % a.Sq;
+  const int G = a.Hq / a.Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int visible = min(a.Sk, a.q_offset + sq + 1);          // causal limit for this query row
+  const int per = (visible + a.splits - 1) / a.splits;
+  const int j0 = split * per, j1 = min(visible, j0 + per);
+
+  __shared__ float s_m[kDecWarps][kMaxGroup], s_l[kDecWarps][kMaxGroup];
+  __shared__ float s_acc[kDecWarps][kMaxGroup][HD];
+
+  float qv[kMaxGroup][E];
+  const __nv_bfloat16* qrow = a.q + (long long)bs * a.ldq + (long long)g * G * HD;
+#pragma unroll
+  for (int h = 0; h < kMaxGroup; ++h)
+#pragma unroll
+    for (int e = 0; e < E; ++e) qv[h][e] = (h < G) ? __bfloat162float(qrow[h * HD + lane * E + e]) * a.scale : 0.0f;
+
+  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][E];
+#pragma unroll
+  for (int h = 0; h < kMaxGroup; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[h][e] = 0.0f;
+  }
+  const __nv_bfloat16* kb = a.k + (long long)b * a.kv_batch_stride + (long long)g * HD + lane * E;
+  const __nv_bfloat16* vb = a.v + (long long)b * a.kv_batch_stride + (long long)g * HD + lane * E;
+
+  for (int blk = j0 + warp * 32; blk < j1; blk += kDecWarps * 32) {
+    const int nk = min(32, j1 - blk);
+    // ---- scores of the block: lane j keeps key j's score for every grouped head
+    float sc[kMaxGroup];
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) sc[h] = -INFINITY;
+#pragma unroll 4
+    for (int j = 0; j < nk; ++j) {
+      float kf[E];
+      const __nv_bfloat16* kr = kb + (long long)(blk + j) * a.ldkv;
+      if (E == 4) {
+        const uint2 u = *reinterpret_cast<const uint2*>(kr);
+        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        kf[0] = p0.x; kf[1] = p0.y; kf[E - 2] = p1.x; kf[E - 1] = p1.y;
+      } else {
+        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kr));
+        kf[0] = p0.x; kf[1] = p0.y;
+      }
+#pragma unroll
+      for (int h = 0; h < kMaxGroup; ++h) {
+        if (h < G) {
+          float d = 0.0f;
+#pragma unroll
+          for (int e = 0; e < E; ++e) d = fmaf(qv[h][e], kf[e], d);
+          d = warp_sum(d);
+          if (lane == j) sc[h] = d;
+        }
+      }
+    }
+    // ---- block softmax statistics and rescale
+    float p[kMaxGroup];
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) {
+      if (h < G) {
+        const float bm = warp_max(sc[h]);
+        const float nm = fmaxf(m[h], bm);
+        const float corr = __expf(m[h] - nm);           // 0 on the first block (m = -inf)
+        p[h] = lane < nk ? __expf(sc[h] - nm) : 0.0f;
+        l[h] = l[h] * corr + warp_sum(p[h]);
+        m[h] = nm;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[h][e] *= corr;
+      } else {
+        p[h] = 0.0f;
+      }
+    }
+    // ---- P.V: broadcast key j's probabilities, every lane accumulates its dims
+#pragma unroll 4
+    for (int j = 0; j < nk; ++j) {
+      float vf[E];
+      const __nv_bfloat16* vr = vb + (long long)(blk + j) * a.ldkv;
+      if (E == 4) {
+        const uint2 u = *reinterpret_cast<const uint2*>(vr);
+        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        vf[0] = p0.x; vf[1] = p0.y; vf[E - 2] = p1.x; vf[E - 1] = p1.y;
+      } else {
+        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr));
+        vf[0] = p0.x; vf[1] = p0.y;
+      }
+#pragma unroll
+      for (int h = 0; h < kMaxGroup; ++h) {
+        if (h < G) {
+          const float pj = __shfl_sync(0xffffffffu, p[h], j);
+#pragma unroll
+          for (int e = 0; e < E; ++e) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
+        }
+      }
+    }
+  }
+  // ---- merge the warps of the CTA (fixed order)
+#pragma unroll
+  for (int h = 0; h < kMaxGroup; ++h) {
+    if (h < G) {
+      if (lane == 0) {
+        s_m[warp][h] = m[h];
+        s_l[warp][h] = l[h];
+      }
+#pragma unroll
+      for (int e = 0; e < E; ++e) s_acc[warp][h][lane * E + e] = acc[h][e];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int h = idx / HD, d = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, s_m[w][h]);
+    float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float c = s_m[w][h] == -INFINITY ? 0.0f : __expf(s_m[w][h] - mm);
+      ll += s_l[w][h] * c;
+      oo += s_acc[w][h][d] * c;
+    }
+    if (a.splits == 1) {
+      a.o[(long long)bs * a.ldo + (long long)(g * G + h) * HD + d] = __float2bfloat16(ll > 0.0f ? oo / ll : 0.0f);
+    } else {
+      float* w = a.ws + ((((long long)bs * a.Hkv + g) * a.splits + split) * G + h) * (HD + 2);
+      w[d] = oo;
+      if (d == 0) {
+        w[HD] = mm;
+        w[HD + 1] = ll;
+      }
+    }
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_merge_kernel(const DecodeArgs a) {
+  const int G = a.Hq / a.Hkv;
+  const int hq = blockIdx.x, bs = blockIdx.y;
+  const int g = hq / G, h = hq % G;
+  const float* base = a.ws + (((long long)bs * a.Hkv + g) * a.splits * G + h) * (HD + 2);
+  const long long stride = (long long)G * (HD + 2);
+  float mm = -INFINITY;
+  for (int s = 0; s < a.splits; ++s) mm = fmaxf(mm, base[s * stride + HD]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float ll = 0.0f, oo = 0.0f;
+    for (int s = 0; s < a.splits; ++s) {
+      const float ms = base[s * stride + HD];
+      const float c = ms == -INFINITY ? 0.0f : __expf(ms - mm);
+      ll += base[s * stride + HD + 1] * c;
+      oo += base[s * stride + d] * c;
+    }
+    a.o[(long long)bs * a.ldo + (long long)hq * HD + d] = __float2bfloat16(ll > 0.0f ? oo / ll : 0.0f);
+  }
+}
+
+// Rotary embedding (half-split form) on the Q and K column blocks of a fused projection row, K / V written straight
+// into the cache at their absolute positions.  Grid: one CTA per (row, head) group; threads over the head dimension.
+//   qkv row layout: [Hq * hd | Hkv * hd | Hkv * hd];  q is rotated in place (the attention kernel reads it there).
+template <int HD>
+__global__ void __launch_bounds__(128)
+rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, __nv_bfloat16* __restrict__ kc,
+                      __nv_bfloat16* __restrict__ vc, long long ldkv, long long kv_batch_stride, int B, int S, int Hq,
+                      int Hkv, int pos0, int rotary_dim, float base, int cap) {
+  const int row = blockIdx.x;                // b * S + s
+  const int b = row / S, s = row % S;
+  const int pos = pos0 + s;
+  if (pos >= cap) return;
+  __nv_bfloat16* r = qkv + (long long)row * ld;
+  const int half = rotary_dim / 2;
+  const int heads = Hq + 2 * Hkv;
+  for (int idx = threadIdx.x; idx < heads * (HD / 2); idx += blockDim.x) {
+    const int h = idx / (HD / 2), i = idx % (HD / 2);
+    // pair (i, i + half) inside the rotary part; dims >= rotary_dim pass through (handled as a pair (d0, d1) with
+    // d0 = rotary_dim + 2 * (i - half), d1 = d0 + 1 so that every element is visited exactly once)
+    int d0, d1;
+    bool rot;
+    if (i < half) { d0 = i; d1 = i + half; rot = true; }
+    else { d0 = rotary_dim + 2 * (i - half); d1 = d0 + 1; rot = false; }
+    __nv_bfloat16* src = r + (long long)h * HD;
+    float x0 = __bfloat162float(src[d0]), x1 = __bfloat162float(src[d1]);
+    const bool is_v = h >= Hq + Hkv;
+    if (rot && !is_v) {
+      const float inv = powf(base, -2.0f * (float)i / (float)rotary_dim);
+      float sn, cs;
+      sincosf((float)pos * inv, &sn, &cs);
+      const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
+      x0 = y0;
+      x1 = y1;
+    }
+    if (h < Hq) {
+      src[d0] = __float2bfloat16(x0);
+      src[d1] = __float2bfloat16(x1);
+    } else {
+      const int g = is_v ? h - Hq - Hkv : h - Hq;
+      __nv_bfloat16* dst = (is_v ? vc : kc) + (long long)b * kv_batch_stride + (long long)pos * ldkv + (long long)g * HD;
+      dst[d0] = __float2bfloat16(x0);
+      dst[d1] = __float2bfloat16(x1);
+    }
+  }
+}
+
+}  // namespace dptb
+
+using namespace dptb;
+
+struct DptbDecodeArgs {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* ws;
+  long long ws_floats;
+  long long ldq, ldkv, ldo, kv_batch_stride;
+  int B, Sq, Sk, Hq, Hkv, head_dim, splits, q_offset;
+  float scale;
+};
+
+// Floats of workspace needed for a given split count.
+extern "C" long long dptb_attn_decode_ws_floats(int B, int Sq, int Hq, int head_dim, int splits) {
+  return splits <= 1 ? 0 : (long long)B * Sq * Hq * splits * (head_dim + 2);
+}
+// Split count that fills the GPU: about two CTAs per SM, at least 256 keys per CTA.
+extern "C" int dptb_attn_decode_splits(int B, int Sq, int Hkv, int Sk) {
+  const int base = B * Sq * Hkv;
+  int s = (2 * sm_count() + base - 1) / base;
+  const int cap = (Sk + 255) / 256;
+  if (s > cap) s = cap;
+  if (s > 64) s = 64;
+  return s < 1 ? 1 : s;
+}
+
+extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
+  auto st = static_cast<cudaStream_t>(stream);
+  if (h->B <= 0 || h->Sq <= 0 || h->Sk <= 0) return 0;
+  if (h->Hkv <= 0 || h->Hq % h->Hkv || h->Hq / h->Hkv > kMaxGroup) return kErrUnsupported;
+  if (h->head_dim != 64 && h->head_dim != 128) return kErrUnsupported;
+  const int E = h->head_dim / 32;
+  if ((h->ldkv % E) || (h->kv_batch_stride % E) || (reinterpret_cast<uintptr_t>(h->k) & (2 * E - 1)) ||
+      (reinterpret_cast<uintptr_t>(h->v) & (2 * E - 1)))
+    return kErrBadShape;
+  DecodeArgs a;
+  a.q = static_cast<const __nv_bfloat16*>(h->q);
+  a.k = static_cast<const __nv_bfloat16*>(h->k);
+  a.v = static_cast<const __nv_bfloat16*>(h->v);
+  a.o = static_cast<__nv_bfloat16*>(h->o);
+  a.ws = h->ws;
+  a.ldq = h->ldq; a.ldkv = h->ldkv; a.ldo = h->ldo; a.kv_batch_stride = h->kv_batch_stride;
+  a.B = h->B; a.Sq = h->Sq; a.Sk = h->Sk; a.Hq = h->Hq; a.Hkv = h->Hkv;
+  a.splits = h->splits < 1 ? 1 : h->splits;
+  a.q_offset = h->q_offset; a.scale = h->scale;
+  if (a.splits > 1 && (!a.ws || h->ws_floats < dptb_attn_decode_ws_floats(a.B, a.Sq, a.Hq, h->head_dim, a.splits)))
+    return kErrTooLarge;
+  dim3 grid(a.splits, a.Hkv, a.B * a.Sq);
+  if (h->head_dim == 128) attn_decode_kernel<128><<<grid, kDecWarps * 32, 0, st>>>(a);
+  else                    attn_decode_kernel<64><<<grid, kDecWarps * 32, 0, st>>>(a);
+  DPTB_CUDA_OK(cudaGetLastError());
+  if (a.splits > 1) {
+    dim3 mg(a.Hq, a.B * a.Sq);
+    if (h->head_dim == 128) attn_decode_merge_kernel<128><<<mg, 128, 0, st>>>(a);
+    else                    attn_decode_merge_kernel<64><<<mg, 128, 0, st>>>(a);
+    return counted(2, (int)cudaGetLastError());
+  }
+  return counted(1, (int)cudaGetLastError());
+}
+
+extern "C" int dptb_rope_kv_append(void* qkv, long long ld, void* kc, void* vc, long long ldkv,
+                                   long long kv_batch_stride, int B, int S, int Hq, int Hkv, int head_dim, int pos0,
+                                   int rotary_dim, float base, int cap, void* stream) {
+  auto st = static_cast<cudaStream_t>(stream);
+  if (B <= 0 || S <= 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || pos0 < 0 || pos0 + S > cap) return kErrBadShape;
+  auto* q = static_cast<__nv_bfloat16*>(qkv);
+  auto* k = static_cast<__nv_bfloat16*>(kc);
+  auto* v = static_cast<__nv_bfloat16*>(vc);
+  if (head_dim == 128)
+    rope_kv_append_kernel<128><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap);
+  else if (head_dim == 64)
+    rope_kv_append_kernel<64><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap);
+  else
+    return kErrUnsupported;
+  return counted(1, (int)cudaGetLastError());
+}

@@ -22,12 +22,12 @@
 #include <cuda_bf16.h>
 
 #include "common/host.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 #include "common/reduce.cuh"
 
 namespace dptb {
 
-constexpr int kMaxRanks = 8;
 constexpr int kDpThreads = 512;
 
 struct DpArgs {
@@ -46,53 +46,6 @@ struct DpArgs {
 __device__ __forceinline__ long long pad_ready(int nb, int b, int r) { return ((long long)b * kMaxRanks + r); }
 __device__ __forceinline__ long long pad_done(int nb, int b, int r) { return ((long long)(nb + b) * kMaxRanks + r); }
 __device__ __forceinline__ long long pad_sumsq(int nb, int b, int r) { return ((long long)(2 * nb + b) * kMaxRanks + r); }
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Bounded wait for *p >= target.  Returns false (and records the failure) when it gives up.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
-  uint64_t t0 = 0;
-  uint32_t spins = 0;
-  while ((int32_t)(ld_acquire_sys(p) - target) < 0) {
-    if ((++spins & 0x3f) == 0) {
-      const uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
-        report_error(kWaitFlagTimeout);
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc_addr)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void multimem_st_bf16x8(void* mc_addr, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_cg_v4(void* p, const uint4& v) {
-  asm volatile("st.global.cg.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
 template <bool NVLS>
 __global__ void __launch_bounds__(kDpThreads)

@@ -17,11 +17,38 @@
 #include <cuda_bf16.h>
 
 #include "common/host.h"
+#include "common/peer.cuh"
 #include "common/ptx.cuh"
 
 namespace dptb {
 
 __device__ int g_status[4] = {0, 0, 0, 0};
+
+// Tensor-parallel all-reduce epilogue (row-parallel Linear: every rank holds a K-slice of the weight and produces a
+// partial [M, N]; the sum over ranks, plus bias / residual, must reach every rank).  world == 0 switches it off.
+//
+// All ranks launch the same grid over the same tiles.  A CTA stores the bf16 partial of tile t into this rank's
+// `partial` buffer (layout [tile][64-column chunk][128 rows][64]), then raises ready[t][rank] in the flag array of the
+// tile's owner, rank t % world.  On the owner, the epilogue warps of the CTA that computed tile t wait (bounded) for
+// all `world` flags, sum the partials in rank order -- one multimem.ld_reduce per 16 bytes through the NVSwitch when a
+// multicast mapping exists, else one peer load per rank -- add bias and residual, and write the result into every
+// rank's output (multimem.st, else one peer store per rank).  The MMA warp meanwhile works on the next tile in the
+// other TMEM accumulator, so NVLink traffic of tile t overlaps the tensor-core work of tile t + gridDim.x.  At the end
+// the last CTA of each rank raises done[rank] on every peer and waits for all done flags: when a rank's kernel
+// completes, its whole output is final.  Epochs count launches, so no flag is ever reset and CUDA graphs can replay.
+struct TpAr {
+  int world, rank;
+  int use_nvls;
+  __nv_bfloat16* partial;                   // local
+  const __nv_bfloat16* peer_partial[kMaxRanks];
+  const __nv_bfloat16* mc_partial;          // multicast view of the partial buffers (or null)
+  __nv_bfloat16* out_peer[kMaxRanks];       // every rank's output [M, ldc]
+  __nv_bfloat16* mc_out;                    // multicast view of the outputs (or null)
+  uint32_t* flags_peer[kMaxRanks];          // every rank's flags: ready[max_tiles][kMaxRanks] then done[kMaxRanks]
+  int max_tiles;
+  uint32_t* epoch;                          // local launch counter
+  unsigned int* exit_counter;               // local, zero between launches
+};
 
 struct GemmParams {
   int M, N, K;
@@ -47,6 +74,7 @@ struct GemmParams {
   int splits, kb_per_split;
   float* ws;
   int* counters;
+  TpAr ar;
 };
 
 // ----------------------------------------------------------------------------- epilogue math
@@ -382,6 +410,69 @@ __device__ __forceinline__ void epilogue_direct_f32(const GemmParams& p, long lo
   }
 }
 
+// ----------------------------------------------------------------------------- all-reduce epilogue helpers
+// Copy the staged 32 x 64 bf16 block (swizzled) into this rank's partial buffer (rows of 128 bytes, contiguous).
+__device__ __forceinline__ void ar_store_partial(const GemmParams& p, const uint8_t* stage, __nv_bfloat16* blk,
+                                                 long long row0, int lane) {
+  const int rg = lane >> 3, cg = lane & 7;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int rl = it * 4 + rg;
+    if (row0 + rl >= p.M) continue;
+    *reinterpret_cast<uint4*>(blk + rl * 64 + cg * 8) =
+        *reinterpret_cast<const uint4*>(stage + rl * 128 + ((cg ^ (rl & 7)) << 4));
+  }
+}
+// Sum one 32 x 64 block over all ranks (fixed rank order), add bias / residual, write it to every rank's output.
+__device__ __forceinline__ void ar_reduce_block(const GemmParams& p, long long blk_off, long long row0, long long col0,
+                                                int lane) {
+  const int rg = lane >> 3, cg = lane & 7;
+  const long long col = col0 + cg * 8;
+  if (col >= p.N) return;
+  float bias8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (p.bias) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      bias8[e] = p.bias_f32 ? __ldg(static_cast<const float*>(p.bias) + col + e)
+                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + e]);
+  }
+#pragma unroll 2
+  for (int it = 0; it < 8; ++it) {
+    const int rl = it * 4 + rg;
+    const long long row = row0 + rl;
+    if (row >= p.M) continue;
+    const long long off = blk_off + rl * 64 + cg * 8;
+    float v[8];
+    if (p.ar.use_nvls) {
+      unpack8(multimem_ld_reduce_bf16x8(p.ar.mc_partial + off), v);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.0f;
+      for (int r = 0; r < p.ar.world; ++r) {
+        float t[8];
+        unpack8(ld_cg_v4(p.ar.peer_partial[r] + off), t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += t[e];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] += bias8[e];
+    if (p.residual) {
+      float t[8];
+      unpack8(*reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col), t);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += t[e];
+    }
+    const uint4 o = pack8(v);
+    const long long o_off = row * p.ldc + col;
+    if (p.ar.use_nvls) {
+      multimem_st_bf16x8(p.ar.mc_out + o_off, o);
+    } else {
+      for (int r = 0; r < p.ar.world; ++r) st_cg_v4(p.ar.out_peer[r] + o_off, o);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- tensor-core kernel
 constexpr int kBM = 128;
 constexpr int kBK = 64;
@@ -420,6 +511,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int num_units = num_tiles * p.splits;
+  // Launch number of the all-reduce protocol; the word is rewritten only by the last CTA to leave.
+  const uint32_t ar_epoch = p.ar.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u : 0u;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -610,7 +703,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after_sync();
       const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      if (p.splits == 1) {
+      if (p.ar.world > 0) {
+        // Partial tile -> this rank's partial buffer; flag the owner; the owner reduces and broadcasts.
+        __nv_bfloat16* ptile = p.ar.partial + (size_t)tile * (BN * kBM);
+#pragma unroll 1
+        for (int c = half; c < BN / 64; c += 2) {
+          if ((long long)n0 + c * 64 >= p.N) break;  // warp-uniform
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          tmem_ld_wait();
+          uint8_t* srow = stage + lane * 128;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t* src = g < 4 ? &r0[g * 8] : &r1[(g - 4) * 8];
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
+            u.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
+            u.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
+            u.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
+            *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = u;
+          }
+          __syncwarp();
+          ar_store_partial(p, stage, ptile + (size_t)c * (64 * kBM) + (size_t)(q * 32) * 64, row0, lane);
+          __syncwarp();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);   // the issuer may start the next tile in this accumulator
+        __threadfence_system();
+        if (!epi_sync()) break;                          // every epilogue warp has written and fenced its blocks
+        const int owner = tile % p.ar.world;
+        if (ew == 0 && lane == 0)
+          st_release_sys(p.ar.flags_peer[owner] + (size_t)tile * kMaxRanks + p.ar.rank, ar_epoch);
+        if (owner == p.ar.rank) {
+          bool ok = true;
+          if (lane < p.ar.world)
+            ok = wait_flag_ge(p.ar.flags_peer[p.ar.rank] + (size_t)tile * kMaxRanks + lane, ar_epoch);
+          if (!__all_sync(0xffffffffu, ok)) {
+            *abort_flag = 1;
+            break;
+          }
+#pragma unroll 1
+          for (int c = half; c < BN / 64; c += 2) {
+            const long long col0 = (long long)n0 + c * 64;
+            if (col0 >= p.N) break;
+            ar_reduce_block(p, (long long)tile * (BN * kBM) + (long long)c * (64 * kBM) + (long long)(q * 32) * 64, row0,
+                            col0, lane);
+          }
+        }
+      } else if (p.splits == 1) {
 #pragma unroll 1
         for (int c = half; c < BN / 64; c += 2) {
           const long long col0 = (long long)n0 + c * 64;
@@ -693,6 +835,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+  if (p.ar.world > 0 && threadIdx.x == 0) {
+    // This rank's output is final once every rank has finished the tiles it owns.
+    __threadfence_system();
+    if (atomicAdd(p.ar.exit_counter, 1u) == gridDim.x - 1) {
+      *p.ar.exit_counter = 0;
+      __threadfence_system();
+      const size_t done0 = (size_t)p.ar.max_tiles * kMaxRanks;
+      for (int r = 0; r < p.ar.world; ++r) st_release_sys(p.ar.flags_peer[r] + done0 + p.ar.rank, ar_epoch);
+      for (int r = 0; r < p.ar.world; ++r)
+        if (!wait_flag_ge(p.ar.flags_peer[p.ar.rank] + done0 + r, ar_epoch)) break;
+      *p.ar.epoch = ar_epoch;
+    }
   }
 }
 
@@ -780,11 +935,29 @@ struct DptbGemmArgs {
   int num_counters;
 };
 
-extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
+// Peer-memory description of the all-reduce epilogue (see TpAr).  `partial_elems` / `max_tiles` are capacities that
+// the launcher checks against the tiling it picks.
+struct DptbTpArArgs {
+  int world, rank, use_nvls, max_tiles;
+  void* partial;
+  long long partial_elems;
+  const void* peer_partial[kMaxRanks];
+  const void* mc_partial;
+  void* out_peer[kMaxRanks];
+  void* mc_out;
+  void* flags_peer[kMaxRanks];
+  void* epoch;
+  void* exit_counter;
+};
+// 32-bit words of a flag array for `max_tiles` tiles.
+extern "C" long long dptb_tp_flag_words(int max_tiles) { return ((long long)max_tiles + 1) * kMaxRanks; }
+
+static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (a->M <= 0 || a->N <= 0) return 0;
   if (a->K < 0) return kErrBadShape;
   GemmParams p;
+  p.ar.world = 0;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.C = a->C; p.ldc = a->ldc;
   p.bias = a->bias; p.bias_f32 = a->bias_f32;
@@ -802,6 +975,12 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
              (!p.aux_out || (al16(p.aux_out) && p.ld_aux_out % 8 == 0)) &&
              (!p.aux_in || (al16(p.aux_in) && p.ld_aux_in % 8 == 0));
 
+  if (ar) {
+    // The all-reduce epilogue exists on the tensor-core path only and moves whole 16-byte groups.
+    if (!tc_ok || !p.vec_ok || (a->N % 8) || a->out_f32 || a->act || a->aux_out || a->aux_in || a->accumulate)
+      return kErrUnsupported;
+    if (ar->world < 1 || ar->world > kMaxRanks || ar->rank < 0 || ar->rank >= ar->world) return kErrBadShape;
+  }
   if (!tc_ok) {
     p.tiles_m = p.tiles_n = p.num_kb = 0;
     p.splits = 1; p.kb_per_split = 0; p.ws = nullptr; p.counters = nullptr;
@@ -836,6 +1015,7 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
       const int tiles = tm * ((a->N + cand_bn - 1) / cand_bn);
       for (int sp = 1; sp <= 8; ++sp) {
         if (a->splits >= 1 && sp != a->splits) continue;
+        if (ar && sp > 1) break;
         if (sp > 1) {
           if (!a->ws || !a->counters || tiles > a->num_counters) break;
           if ((long long)tiles * sp * cand_bn * kBM * 4 > a->ws_bytes) break;
@@ -864,6 +1044,23 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
   }
   p.ws = static_cast<float*>(a->ws);
   p.counters = a->counters;
+  if (ar) {
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    if (p.splits != 1 || tiles > ar->max_tiles || tiles * bn * kBM > ar->partial_elems) return kErrTooLarge;
+    p.ar.world = ar->world; p.ar.rank = ar->rank;
+    p.ar.use_nvls = (ar->use_nvls && ar->mc_partial && ar->mc_out) ? 1 : 0;
+    p.ar.partial = static_cast<__nv_bfloat16*>(ar->partial);
+    p.ar.mc_partial = static_cast<const __nv_bfloat16*>(ar->mc_partial);
+    p.ar.mc_out = static_cast<__nv_bfloat16*>(ar->mc_out);
+    for (int r = 0; r < kMaxRanks; ++r) {
+      p.ar.peer_partial[r] = static_cast<const __nv_bfloat16*>(ar->peer_partial[r]);
+      p.ar.out_peer[r] = static_cast<__nv_bfloat16*>(ar->out_peer[r]);
+      p.ar.flags_peer[r] = static_cast<uint32_t*>(ar->flags_peer[r]);
+    }
+    p.ar.max_tiles = ar->max_tiles;
+    p.ar.epoch = static_cast<uint32_t*>(ar->epoch);
+    p.ar.exit_counter = static_cast<unsigned int*>(ar->exit_counter);
+  }
 
   CUtensorMap tmA, tmB;
   int rc;
@@ -882,6 +1079,15 @@ extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) {
   if (amn && !bmn) return DPTB_LAUNCH(true, false);
   return DPTB_LAUNCH(true, true);
 #undef DPTB_LAUNCH
+}
+
+extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) { return gemm_impl(a, nullptr, stream_v); }
+// Row-parallel Linear of a tensor-parallel group in ONE kernel: tcgen05 GEMM of this rank's K-slice, then the sum over
+// ranks (+ bias, + residual) through NVLink peer memory, delivered to every rank's `out`.  Every rank must call it with
+// the same shapes; C of the argument block is ignored (the result goes to ar->out_peer / ar->mc_out with row stride ldc).
+extern "C" int dptb_gemm_allreduce(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream_v) {
+  if (!ar) return kErrBadShape;
+  return gemm_impl(a, ar, stream_v);
 }
 
 // Status word access ------------------------------------------------------------------------------

@@ -1,0 +1,158 @@
+"""Tensor parallelism over NVLink peer memory: host side of the fused GEMM + all-reduce kernel (``csrc/gemm.cu``,
+``dptb_gemm_allreduce``).
+
+The reference has no tensor parallelism; its per-head ``Linear`` lists make head sharding natural
+(lib/core/nn/attention/multi_head_attention.dart:58-94) but nothing shards.  Here QKV / gate / up are column-parallel
+(each rank holds a slice of the output features, no communication), ``wo`` / ``down`` are row-parallel: every rank
+multiplies its K-slice and the partial sums are reduced across ranks *inside the GEMM kernel's epilogue*, tile by tile,
+through symmetric memory (``torch.distributed._symmetric_memory`` allocates and exchanges the buffers; no collective
+library runs on the data path).  The reduced rows, plus bias and residual, land in every rank's copy of a symmetric
+activation buffer.
+
+``TpComm`` owns the symmetric buffers of one group: ``num_bufs`` activation buffers ``[max_rows, width]`` (the residual
+stream ping-pongs between them), one partial-tile buffer, one flag array, and the local epoch / exit counters.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as N
+from ..ops import kernels as K
+
+MAX_RANKS = 8
+c_void_p, c_int, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+
+
+class TpArArgs(ctypes.Structure):
+    _fields_ = [("world", c_int), ("rank", c_int), ("use_nvls", c_int), ("max_tiles", c_int),
+                ("partial", c_void_p), ("partial_elems", c_ll),
+                ("peer_partial", c_void_p * MAX_RANKS), ("mc_partial", c_void_p),
+                ("out_peer", c_void_p * MAX_RANKS), ("mc_out", c_void_p),
+                ("flags_peer", c_void_p * MAX_RANKS), ("epoch", c_void_p), ("exit_counter", c_void_p)]
+
+
+def _declare(lib):
+    lib.dptb_tp_flag_words.argtypes = [c_int]
+    lib.dptb_tp_flag_words.restype = c_ll
+    lib.dptb_gemm_allreduce.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpArArgs), c_void_p]
+    lib.dptb_gemm_allreduce.restype = c_int
+
+
+def shard_range(total: int, rank: int, world: int):
+    """Contiguous equal split; ``total`` must divide."""
+    if total % world:
+        raise ValueError(f"cannot split {total} over {world} ranks")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+class TpComm:
+    def __init__(self, max_rows: int, width: int, group=None, num_bufs: int = 2, device=None,
+                 use_nvls: Optional[bool] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.lib = N.load()
+        _declare(self.lib)
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > MAX_RANKS:
+            raise ValueError(f"tensor parallelism supports up to {MAX_RANKS} ranks per node")
+        if width % 8:
+            raise ValueError("TpComm: width must be a multiple of 8")
+        dev = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.device, self.max_rows, self.width = dev, max_rows, width
+        gname = self.group.group_name
+        rows_pad = (max_rows + 127) // 128 * 128
+        width_pad = (width + 255) // 256 * 256
+        self.max_tiles = (rows_pad // 128) * (width_pad // 128)
+        self.partial = symm_mem.empty(rows_pad * width_pad, dtype=torch.bfloat16, device=dev)
+        self.partial.zero_()
+        self._h_partial = symm_mem.rendezvous(self.partial, group=gname)
+        self.bufs: List[torch.Tensor] = []
+        self._h_bufs = []
+        for _ in range(num_bufs):
+            b = symm_mem.empty(max_rows, width, dtype=torch.bfloat16, device=dev)
+            b.zero_()
+            self.bufs.append(b)
+            self._h_bufs.append(symm_mem.rendezvous(b, group=gname))
+        words = int(self.lib.dptb_tp_flag_words(self.max_tiles))
+        self.flags = symm_mem.empty(words, dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        self._h_flags = symm_mem.rendezvous(self.flags, group=gname)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.exit_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        mc_ok = all(int(getattr(h, "multicast_ptr", 0) or 0) != 0 for h in [self._h_partial] + self._h_bufs)
+        want = mc_ok if use_nvls is None else use_nvls
+        env = os.environ.get("DPTB200_TP_NVLS")
+        if env is not None:
+            want = env not in ("0", "false", "False")
+        self.use_nvls = bool(want and mc_ok)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)          # every rank's flags are zero before anyone signals
+        self._ar = []
+        for i in range(num_bufs):
+            a = TpArArgs()
+            a.world, a.rank, a.use_nvls, a.max_tiles = self.world, self.rank, int(self.use_nvls), self.max_tiles
+            a.partial, a.partial_elems = self.partial.data_ptr(), self.partial.numel()
+            for r in range(MAX_RANKS):
+                a.peer_partial[r] = int(self._h_partial.buffer_ptrs[r]) if r < self.world else None
+                a.out_peer[r] = int(self._h_bufs[i].buffer_ptrs[r]) if r < self.world else None
+                a.flags_peer[r] = int(self._h_flags.buffer_ptrs[r]) if r < self.world else None
+            a.mc_partial = int(self._h_partial.multicast_ptr) if self.use_nvls else None
+            a.mc_out = int(self._h_bufs[i].multicast_ptr) if self.use_nvls else None
+            a.epoch, a.exit_counter = self.epoch.data_ptr(), self.exit_counter.data_ptr()
+            self._ar.append(a)
+
+    def buffer(self, index: int, rows: int) -> torch.Tensor:
+        """First ``rows`` rows of activation buffer ``index`` (this rank's copy)."""
+        if rows > self.max_rows:
+            raise ValueError(f"TpComm: {rows} rows exceed the buffer's {self.max_rows}")
+        return self.bufs[index][:rows]
+
+    def gemm_allreduce(self, x: torch.Tensor, w_shard: torch.Tensor, out_index: int,
+                       residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``out = sum_over_ranks(x_r @ w_r^T) (+ bias) (+ residual)`` written into activation buffer ``out_index`` of
+        EVERY rank.  ``x``: ``[M, K/world]`` bf16 (this rank's slice of the features), ``w_shard``: ``[N, K/world]``.
+        ``residual`` (the same on all ranks) must not alias the output buffer."""
+        M, Kr = x.shape
+        Nn = w_shard.shape[0]
+        if w_shard.shape[1] != Kr:
+            raise ValueError(f"gemm_allreduce: inner dimensions differ ({Kr} vs {w_shard.shape[1]})")
+        if Nn != self.width:
+            raise ValueError(f"gemm_allreduce: output width {Nn} != buffer width {self.width}")
+        out = self.buffer(out_index, M)
+        if residual is not None and residual.data_ptr() == out.data_ptr():
+            raise ValueError("gemm_allreduce: residual must live in a different buffer than the output")
+        for t in (x, w_shard):
+            if t.dtype != torch.bfloat16 or t.stride(-1) != 1:
+                raise TypeError("gemm_allreduce: operands must be bfloat16 with a contiguous last axis")
+        g = N.GemmArgs()
+        g.A, g.B, g.C = x.data_ptr(), w_shard.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = x.stride(0), w_shard.stride(0), out.stride(0)
+        g.M, g.N, g.K = M, Nn, Kr
+        g.trans_a, g.trans_b = 0, 1
+        g.alpha, g.splits = 1.0, 1
+        if bias is not None:
+            g.bias, g.bias_f32 = bias.data_ptr(), int(bias.dtype == torch.float32)
+        if residual is not None:
+            if residual.dtype != torch.bfloat16 or residual.shape[0] != M or residual.shape[1] < Nn:
+                raise ValueError("gemm_allreduce: residual has the wrong shape or dtype")
+            g.residual, g.ldr = residual.data_ptr(), residual.stride(0)
+        N.check(self.lib.dptb_gemm_allreduce(ctypes.byref(g), ctypes.byref(self._ar[out_index]), N.stream_ptr()),
+                "gemm_allreduce")
+        return out
+
+
+def reference_row_parallel(x_full: torch.Tensor, w_full: torch.Tensor, residual=None, bias=None) -> torch.Tensor:
+    """fp32 oracle of what ``gemm_allreduce`` leaves on every rank."""
+    y = x_full.float() @ w_full.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if residual is not None:
+        y = y + residual.float()
+    return y

@@ -1,0 +1,29 @@
+"""Multi-GPU tests of the tensor-parallel path (need >= 2 GPUs; run as child processes, one rank per GPU)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(script: str, mode: str, nproc: int = 2, port: int = 29543, ok: str = "ok"):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script), mode]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert ok in proc.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_allreduce_peer_loads():
+    _run("tp_worker.py", "p2p", port=29543, ok="tp_worker ok")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gemm_allreduce_auto_multimem():
+    _run("tp_worker.py", "auto", port=29544, ok="tp_worker ok")
