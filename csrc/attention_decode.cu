@@ -35,6 +35,9 @@ struct DecodeArgs {
   int B, Sq, Sk, Hq, Hkv, splits;
   int q_offset;              // absolute position of query row 0 (causal: query i sees keys <= q_offset + i)
   float scale;
+  const int* pos_ptr;        // when set: q_offset = *pos_ptr and Sk = q_offset + Sq (device-resident position, so a
+                             // captured CUDA graph can be replayed as the sequence grows)
+  int cap;                   // cache rows per sequence: no key at or beyond it is ever read
 };
 
 template <int HD>
@@ -45,7 +48,9 @@ attn_decode_kernel(const DecodeArgs a) {
   const int b = bs / a.Sq, sq = bs % a.Sq;
   const int G = a.Hq / a.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int visible = min(a.Sk, a.q_offset + sq + 1);          // causal limit for this query row
+  const int q_off = a.pos_ptr ? *a.pos_ptr : a.q_offset;
+  const int sk = a.pos_ptr ? q_off + a.Sq : a.Sk;
+  const int visible = min(min(sk, a.cap), q_off + sq + 1);     // causal limit for this query row
   const int per = (visible + a.splits - 1) / a.splits;
   const int j0 = split * per, j1 = min(visible, j0 + per);
 
@@ -208,10 +213,10 @@ template <int HD>
 __global__ void __launch_bounds__(128)
 rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, __nv_bfloat16* __restrict__ kc,
                       __nv_bfloat16* __restrict__ vc, long long ldkv, long long kv_batch_stride, int B, int S, int Hq,
-                      int Hkv, int pos0, int rotary_dim, float base, int cap) {
+                      int Hkv, int pos0, int rotary_dim, float base, int cap, const int* __restrict__ pos_ptr) {
   const int row = blockIdx.x;                // b * S + s
   const int b = row / S, s = row % S;
-  const int pos = pos0 + s;
+  const int pos = (pos_ptr ? *pos_ptr : pos0) + s;
   if (pos >= cap) return;
   __nv_bfloat16* r = qkv + (long long)row * ld;
   const int half = rotary_dim / 2;
@@ -261,6 +266,8 @@ struct DptbDecodeArgs {
   long long ldq, ldkv, ldo, kv_batch_stride;
   int B, Sq, Sk, Hq, Hkv, head_dim, splits, q_offset;
   float scale;
+  const int* pos_ptr;
+  int cap;
 };
 
 // Floats of workspace needed for a given split count.
@@ -296,6 +303,7 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
   a.B = h->B; a.Sq = h->Sq; a.Sk = h->Sk; a.Hq = h->Hq; a.Hkv = h->Hkv;
   a.splits = h->splits < 1 ? 1 : h->splits;
   a.q_offset = h->q_offset; a.scale = h->scale;
+  a.pos_ptr = h->pos_ptr; a.cap = h->cap > 0 ? h->cap : h->Sk;
   if (a.splits > 1 && (!a.ws || h->ws_floats < dptb_attn_decode_ws_floats(a.B, a.Sq, a.Hq, h->head_dim, a.splits)))
     return kErrTooLarge;
   dim3 grid(a.splits, a.Hkv, a.B * a.Sq);
@@ -313,17 +321,18 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
 
 extern "C" int dptb_rope_kv_append(void* qkv, long long ld, void* kc, void* vc, long long ldkv,
                                    long long kv_batch_stride, int B, int S, int Hq, int Hkv, int head_dim, int pos0,
-                                   int rotary_dim, float base, int cap, void* stream) {
+                                   int rotary_dim, float base, int cap, const int* pos_ptr, void* stream) {
   auto st = static_cast<cudaStream_t>(stream);
   if (B <= 0 || S <= 0) return 0;
-  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || pos0 < 0 || pos0 + S > cap) return kErrBadShape;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || pos0 < 0 || (!pos_ptr && pos0 + S > cap))
+    return kErrBadShape;
   auto* q = static_cast<__nv_bfloat16*>(qkv);
   auto* k = static_cast<__nv_bfloat16*>(kc);
   auto* v = static_cast<__nv_bfloat16*>(vc);
   if (head_dim == 128)
-    rope_kv_append_kernel<128><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap);
+    rope_kv_append_kernel<128><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap, pos_ptr);
   else if (head_dim == 64)
-    rope_kv_append_kernel<64><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap);
+    rope_kv_append_kernel<64><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap, pos_ptr);
   else
     return kErrUnsupported;
   return counted(1, (int)cudaGetLastError());

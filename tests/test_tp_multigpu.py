@@ -27,3 +27,9 @@ def test_fused_gemm_allreduce_peer_loads():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_gemm_allreduce_auto_multimem():
     _run("tp_worker.py", "auto", port=29544, ok="tp_worker ok")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("hd", ["64", "128"])
+def test_tp_llama_engine_matches_whole_model(hd):
+    _run("tp_llama_worker.py", hd, port=29545 + (hd == "128"), ok="tp_llama_worker ok")
