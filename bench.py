@@ -150,7 +150,8 @@ def run_ours(args):
     reducer = None
     if world > 1:
         from dart_pytorch_b200.parallel.dp import GradReducer
-        reducer = GradReducer(opt.arena, world)
+        overlap = os.environ.get("DPTB200_DP_OVERLAP", "1") not in ("0", "false", "False")
+        reducer = GradReducer(opt.arena, world, overlap=overlap)
     trainer = Trainer(model, opt, sched, clip_norm=1.0, use_graph=not args.no_graph, reducer=reducer)
 
     n_batches = args.warmup + 2 * args.steps
@@ -210,6 +211,7 @@ def run_ours(args):
                        "parallelism": f"dp{world}", "optimizer": "adamw lr6e-4 wd0.1 clip1.0 warmup-cosine",
                        "cache_policy": "per-step working set (>2 GB of activations and logits) exceeds the 126 MB L2",
                        "cuda_graph": trainer._graph is not None,
+                       "grad_reduce_overlap": bool(reducer is not None and getattr(reducer, "overlap", False)),
                        "grad_reduce": "none" if reducer is None else
                        (reducer.mode + ("+multimem" if getattr(reducer.impl, "use_nvls", False) else ""))},
             "clocks": clocks,

@@ -39,7 +39,10 @@ def peaks():
     return hbm, tf, src
 
 
-def build_cases(dev):
+def build_cases(dev, want=()):
+    """Cases are built only when their group is selected, so a profiler run of one kernel holds little memory."""
+    def on(group):
+        return not want or any(w in group or group in w for w in want)
     M, D, H, hd, B, S, V = 16384, 768, 12, 64, 16, 1024, 50257
     VP = (V + 127) // 128 * 128
     bf = dict(device=dev, dtype=torch.bfloat16)
@@ -51,6 +54,8 @@ def build_cases(dev):
     cases = {}
 
     def gemm_case(name, m, n, k, ta, tb, **kw):
+        if want and not any(w in name for w in want):
+            return
         a = torch.randn((k, m) if ta else (m, k), **bf)
         b = torch.randn((n, k) if tb else (k, n), **bf)
         c = torch.empty(m, n, **bf)
@@ -79,62 +84,76 @@ def build_cases(dev):
     gemm_case("gemm_proj_wgrad", D, D, M, True, False)
     gemm_case("gemm_8192", 8192, 8192, 8192, False, True)
 
-    _, mean, rstd = K.layernorm_fwd(x, gamma, beta, 1e-5)
+    if on("norm"):
+      _, mean, rstd = K.layernorm_fwd(x, gamma, beta, 1e-5)
+      _, rrstd = K.rmsnorm_fwd(x, gamma, 1e-5)
+    else:
+      mean = rstd = rrstd = None
     cases["norm_fwd"] = (lambda: K.layernorm_fwd(x, gamma, beta, 1e-5), 2 * 2 * M * D, 0.0)
     cases["norm_bwd"] = (lambda: K.layernorm_bwd(x, dy, gamma, mean, rstd, dres=dres), 4 * 2 * M * D, 0.0)
-    _, rrstd = K.rmsnorm_fwd(x, gamma, 1e-5)
     cases["rmsnorm_fwd"] = (lambda: K.rmsnorm_fwd(x, gamma, 1e-5), 2 * 2 * M * D, 0.0)
     cases["rmsnorm_bwd"] = (lambda: K.rmsnorm_bwd(x, dy, gamma, rrstd, dres=dres), 4 * 2 * M * D, 0.0)
 
-    qkv = torch.randn(M, 3 * D, **bf)
-    o = torch.empty(M, D, **bf)
-    q2, k2, v2 = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
-    _, lse = A.attn_fwd(q2, k2, v2, B, S, S, H, H, hd, True, out=o)
-    do = torch.randn(M, D, **bf)
-    dqkv = torch.empty(M, 3 * D, **bf)
-    att_flops = 4.0 * B * H * S * S * hd / 2  # causal: half of the score matrix
-    cases["attn_fwd"] = (lambda: A.attn_fwd(q2, k2, v2, B, S, S, H, H, hd, True, out=o), 2 * 4 * M * D, att_flops)
-    cases["attn_bwd"] = (lambda: A.attn_bwd(q2, k2, v2, o, do, lse, dqkv[:, :D], dqkv[:, D:2 * D], dqkv[:, 2 * D:],
-                                            B, S, S, H, H, hd, True), 2 * 8 * M * D, 2.5 * att_flops)
+    if on("attn"):
+        qkv = torch.randn(M, 3 * D, **bf)
+        o = torch.empty(M, D, **bf)
+        q2, k2, v2 = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
+        _, lse = A.attn_fwd(q2, k2, v2, B, S, S, H, H, hd, True, out=o)
+        do = torch.randn(M, D, **bf)
+        dqkv = torch.empty(M, 3 * D, **bf)
+        att_flops = 4.0 * B * H * S * S * hd / 2  # causal: half of the score matrix
+        cases["attn_fwd"] = (lambda: A.attn_fwd(q2, k2, v2, B, S, S, H, H, hd, True, out=o), 2 * 4 * M * D, att_flops)
+        cases["attn_bwd"] = (lambda: A.attn_bwd(q2, k2, v2, o, do, lse, dqkv[:, :D], dqkv[:, D:2 * D], dqkv[:, 2 * D:],
+                                                B, S, S, H, H, hd, True), 2 * 8 * M * D, 2.5 * att_flops)
+    if on("ce"):
+        logits = torch.randn(M, VP, **bf)
+        tgt = torch.randint(0, V, (M,), device=dev)
+        _, lse_ce = K.ce_fwd(logits, tgt, V)
+        gone = torch.ones(1, device=dev, dtype=torch.float32)
+        cases["ce_fwd"] = (lambda: K.ce_fwd(logits, tgt, V), 2 * M * VP, 0.0)
+        cases["ce_bwd"] = (lambda: K.ce_bwd(logits, tgt, lse_ce, gone, 1.0 / M, V, out=logits, pad_to=VP), 4 * M * VP, 0.0)
 
-    logits = torch.randn(M, VP, **bf)
-    tgt = torch.randint(0, V, (M,), device=dev)
-    _, lse_ce = K.ce_fwd(logits, tgt, V)
-    gone = torch.ones(1, device=dev, dtype=torch.float32)
-    cases["ce_fwd"] = (lambda: K.ce_fwd(logits, tgt, V), 2 * M * VP, 0.0)
-    cases["ce_bwd"] = (lambda: K.ce_bwd(logits, tgt, lse_ce, gone, 1.0 / M, V, out=logits, pad_to=VP), 4 * M * VP, 0.0)
-
-    for cols in (D, 3 * D, 4 * D):
+    for cols in (D, 3 * D, 4 * D) if on("colsum") else ():
         src = torch.randn(M, cols, **bf)
         dst = torch.zeros(cols, **bf)
         cases[f"colsum_{cols}"] = (lambda src=src, dst=dst: K.colsum(src, dst, accumulate=True), 2 * M * cols, 0.0)
 
-    table = torch.randn(V, D, **bf)
-    pos = torch.randn(S, D, **bf)
-    idx = torch.randint(0, V, (M,), device=dev)
-    dtable = torch.zeros(V, D, **bf)
-    cases["embedding_fwd"] = (lambda: K.embedding_fwd(table, idx, pos, 0, S), 2 * 2 * M * D, 0.0)
-    cases["embedding_bwd"] = (lambda: K.embedding_bwd(dtable, idx, dy), 2 * 2 * M * D, 0.0)
-
-    n = 124_500_000
-    p = torch.randn(n, device=dev)           # fp32 master
-    shadow = p.to(torch.bfloat16)            # bf16 working copy
-    g = torch.randn(n, **bf)
-    m1 = torch.zeros(n, device=dev)
-    v1 = torch.zeros(n, device=dev)
-    ctrl = torch.zeros(4, device=dev)
-    ctrl[1] = 1.0
-    ctrl[2] = 1.0
-    cases["grad_norm"] = (lambda: K.grad_norm(g, ctrl, 1.0), 2 * n, 0.0)
-    cases["adam_flat"] = (lambda: K.adam_flat(p, shadow, g, m1, v1, ctrl, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05),
-                          n * (2 + 2 + 4 * 6), 0.0)
-
-    gate = torch.randn(M, 4 * D, **bf)
-    up = torch.randn(M, 4 * D, **bf)
-    sw = torch.empty(M, 4 * D, **bf)
-    cases["swiglu_fwd"] = (lambda: K.swiglu_fwd(gate, up, sw), 3 * 2 * M * 4 * D, 0.0)
-    sm = torch.randn(B * H * 64, S, **bf)
-    cases["softmax_fwd"] = (lambda: K.softmax_fwd(sm), 2 * 2 * sm.numel(), 0.0)
+    if on("embedding"):
+        table = torch.randn(V, D, **bf)
+        pos = torch.randn(S, D, **bf)
+        idx = torch.randint(0, V, (M,), device=dev)
+        dtable = torch.zeros(V, D, **bf)
+        cases["embedding_fwd"] = (lambda: K.embedding_fwd(table, idx, pos, 0, S), 2 * 2 * M * D, 0.0)
+        cases["embedding_bwd"] = (lambda: K.embedding_bwd(dtable, idx, dy), 2 * 2 * M * D, 0.0)
+    if on("adam") or on("grad_norm"):
+        n = 124_500_000
+        p = torch.randn(n, device=dev)           # fp32 master
+        shadow = p.to(torch.bfloat16)            # bf16 working copy
+        g = torch.randn(n, **bf)
+        m1 = torch.zeros(n, device=dev)
+        v1 = torch.zeros(n, device=dev)
+        ctrl = torch.zeros(4, device=dev)
+        ctrl[1] = 1.0
+        ctrl[2] = 1.0
+        cases["grad_norm"] = (lambda: K.grad_norm(g, ctrl, 1.0), 2 * n, 0.0)
+        cases["adam_flat"] = (lambda: K.adam_flat(p, shadow, g, m1, v1, ctrl, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05),
+                              n * (2 + 2 + 4 * 6), 0.0)
+    if on("swiglu") or on("softmax"):
+        gate = torch.randn(M, 4 * D, **bf)
+        up = torch.randn(M, 4 * D, **bf)
+        sw = torch.empty(M, 4 * D, **bf)
+        cases["swiglu_fwd"] = (lambda: K.swiglu_fwd(gate, up, sw), 3 * 2 * M * 4 * D, 0.0)
+        sm = torch.randn(B * H * 64, S, **bf)
+        cases["softmax_fwd"] = (lambda: K.softmax_fwd(sm), 2 * 2 * sm.numel(), 0.0)
+    if on("decode"):
+        from dart_pytorch_b200.ops import decode as Dk
+        Bd, Sk, Hq, Hkv, hdd = 32, 2304, 4, 1, 128                    # one rank of Llama-8B TP=8, batch 32
+        qd = torch.randn(Bd, Hq * hdd, **bf)
+        kc = torch.randn(Bd, Sk, Hkv * hdd, **bf)
+        vc = torch.randn(Bd, Sk, Hkv * hdd, **bf)
+        od = torch.empty(Bd, Hq * hdd, **bf)
+        cases["attn_decode"] = (lambda: Dk.attn_decode(qd, kc, vc, Bd, 1, Sk, Hq, Hkv, hdd, Sk - 1, out=od),
+                                2 * 2 * Bd * Sk * Hkv * hdd, 0.0)
     return cases
 
 
@@ -148,8 +167,8 @@ def main():
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
     hbm, tf, src = peaks()
-    cases = build_cases(dev)
     want = [w for w in args.only.split(",") if w]
+    cases = build_cases(dev, want)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []
     print(f"{'kernel':24s} {'us':>9s} {'GB/s':>8s} {'TF/s':>8s}  frac of {src} peak")

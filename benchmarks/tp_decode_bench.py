@@ -77,8 +77,15 @@ class TorchTPLlama:
             L["k"][b0:b0 + B, :, pos0:pos0 + S] = k
             L["v"][b0:b0 + B, :, pos0:pos0 + S] = v
             kk, vv = L["k"][b0:b0 + B, :, :pos0 + S], L["v"][b0:b0 + B, :, :pos0 + S]
-            o = Fn.scaled_dot_product_attention(q, kk, vv, is_causal=S > 1, enable_gqa=True)
-            part = o.transpose(1, 2).reshape(B, S, self.Hq * hd) @ L["wo"].t()
+            if S == 1:
+                # one new token: the G query heads that share a KV head become G query rows of that head, which lets
+                # the fused SDPA kernels run without materialising repeated keys
+                qg = q.reshape(B, self.Hkv, self.Hq // self.Hkv, hd)
+                o = Fn.scaled_dot_product_attention(qg, kk, vv).reshape(B, 1, self.Hq * hd)
+            else:
+                o = Fn.scaled_dot_product_attention(q, kk, vv, is_causal=True, enable_gqa=True)
+                o = o.transpose(1, 2).reshape(B, S, self.Hq * hd)
+            part = o @ L["wo"].t()
             dist.all_reduce(part, group=self.group)
             x = x + part
             y = Fn.rms_norm(x, (c.embed_dim,), L["n2"], c.rms_norm_eps)

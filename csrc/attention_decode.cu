@@ -8,10 +8,10 @@
 // attention streams each KV row exactly once for all query heads that share it (grouped-query attention).
 //
 // attn_decode_kernel: grid (splits, Hkv, B * Sq).  A CTA owns one (sequence, query position, kv head) and a contiguous
-// chunk of the keys; its 4 warps take 32-key blocks round-robin.  Within a warp each lane holds hd/32 dimensions of the
-// current key / value row (one 256-byte coalesced row read per key for hd = 128), scores of the G = Hq / Hkv grouped
-// heads are reduced with shuffles, the softmax is computed per 32-key block (lane j owns key j) and the block's
-// probabilities are broadcast back for the P.V accumulation.  Partial (max, sum, acc) per (warp -> CTA -> split) are
+// chunk of the keys; its 4 warps take 32-key blocks round-robin.  A key / value row is read by hd/8 lanes with one
+// 16-byte load each (several keys per load instruction, eight loads in flight per lane), scores of the G = Hq / Hkv
+// grouped heads are reduced with shuffles inside those lanes, the softmax is computed per 32-key block (lane j owns
+// key j) and the block's probabilities are fetched back by shuffle for the P.V accumulation.  Partial (max, sum, acc) per (warp -> CTA -> split) are
 // merged in shared memory and, when the keys are split across CTAs, through an fp32 workspace by attn_decode_merge.
 // The kernel is memory-bound by design: the roofline is the KV bytes over HBM bandwidth.
 #include <cuda_bf16.h>
@@ -40,122 +40,146 @@ struct DecodeArgs {
   int cap;                   // cache rows per sequence: no key at or beyond it is ever read
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kDecWarps * 32)
+__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// GP = grouped query heads padded to a power of two (heads >= G carry zero queries).  A key row is covered by
+// LPK = HD / 8 lanes with one 16-byte load each, so one load instruction of the warp fetches 32 / LPK keys; the loads
+// of eight iterations are issued before the first use (4 KB in flight per warp), which is what a latency-bound
+// streaming kernel needs.  Sub-group sg (LPK lanes) walks keys blk + LPK * sg + i, i < LPK: lane l ends up holding the
+// score of key blk + l, so the block softmax is two warp reductions and the probabilities are fetched back by shuffle.
+template <int HD, int GP>
+__global__ void __launch_bounds__(kDecWarps * 32, GP <= 4 ? 3 : 2)
 attn_decode_kernel(const DecodeArgs a) {
-  constexpr int E = HD / 32;                 // dims per lane
+  constexpr int LPK = HD / 8;                // lanes per key
+  constexpr int U = 8;                       // key loads kept in flight per lane
+  static_assert(LPK % U == 0, "sub-group key count must be a multiple of the load batch");
   const int split = blockIdx.x, g = blockIdx.y, bs = blockIdx.z;
   const int b = bs / a.Sq, sq = bs % a.Sq;
   const int G = a.Hq / a.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sl = lane & (LPK - 1), sg0 = lane & ~(LPK - 1);   // lane within the sub-group, first lane of the sub-group
   const int q_off = a.pos_ptr ? *a.pos_ptr : a.q_offset;
   const int sk = a.pos_ptr ? q_off + a.Sq : a.Sk;
   const int visible = min(min(sk, a.cap), q_off + sq + 1);     // causal limit for this query row
   const int per = (visible + a.splits - 1) / a.splits;
   const int j0 = split * per, j1 = min(visible, j0 + per);
 
-  __shared__ float s_m[kDecWarps][kMaxGroup], s_l[kDecWarps][kMaxGroup];
-  __shared__ float s_acc[kDecWarps][kMaxGroup][HD];
+  __shared__ float s_m[kDecWarps][GP], s_l[kDecWarps][GP];
+  __shared__ float s_acc[kDecWarps][GP][HD];
 
-  float qv[kMaxGroup][E];
-  const __nv_bfloat16* qrow = a.q + (long long)bs * a.ldq + (long long)g * G * HD;
+  float qv[GP][8];
+  const __nv_bfloat16* qrow = a.q + (long long)bs * a.ldq + (long long)g * G * HD + sl * 8;
 #pragma unroll
-  for (int h = 0; h < kMaxGroup; ++h)
+  for (int h = 0; h < GP; ++h) {
+    if (h < G) {
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(qrow + h * HD), qv[h]);
 #pragma unroll
-    for (int e = 0; e < E; ++e) qv[h][e] = (h < G) ? __bfloat162float(qrow[h * HD + lane * E + e]) * a.scale : 0.0f;
-
-  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][E];
+      for (int e = 0; e < 8; ++e) qv[h][e] *= a.scale;
+    } else {
 #pragma unroll
-  for (int h = 0; h < kMaxGroup; ++h) {
+      for (int e = 0; e < 8; ++e) qv[h][e] = 0.0f;
+    }
+  }
+  float m[GP], l[GP], acc[GP][8];
+#pragma unroll
+  for (int h = 0; h < GP; ++h) {
     m[h] = -INFINITY;
     l[h] = 0.0f;
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[h][e] = 0.0f;
+    for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
   }
-  const __nv_bfloat16* kb = a.k + (long long)b * a.kv_batch_stride + (long long)g * HD + lane * E;
-  const __nv_bfloat16* vb = a.v + (long long)b * a.kv_batch_stride + (long long)g * HD + lane * E;
+  const __nv_bfloat16* kb = a.k + (long long)b * a.kv_batch_stride + (long long)g * HD + sl * 8;
+  const __nv_bfloat16* vb = a.v + (long long)b * a.kv_batch_stride + (long long)g * HD + sl * 8;
 
   for (int blk = j0 + warp * 32; blk < j1; blk += kDecWarps * 32) {
-    const int nk = min(32, j1 - blk);
-    // ---- scores of the block: lane j keeps key j's score for every grouped head
-    float sc[kMaxGroup];
+    const int key0 = blk + sg0;              // first key of this sub-group
+    // ---- scores: lane l keeps the score of key blk + l
+    float sc[GP];
 #pragma unroll
-    for (int h = 0; h < kMaxGroup; ++h) sc[h] = -INFINITY;
-#pragma unroll 4
-    for (int j = 0; j < nk; ++j) {
-      float kf[E];
-      const __nv_bfloat16* kr = kb + (long long)(blk + j) * a.ldkv;
-      if (E == 4) {
-        const uint2 u = *reinterpret_cast<const uint2*>(kr);
-        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-        const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-        kf[0] = p0.x; kf[1] = p0.y; kf[E - 2] = p1.x; kf[E - 1] = p1.y;
-      } else {
-        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kr));
-        kf[0] = p0.x; kf[1] = p0.y;
+    for (int h = 0; h < GP; ++h) sc[h] = -INFINITY;
+#pragma unroll 1
+    for (int i0 = 0; i0 < LPK; i0 += U) {
+      uint4 kr[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int key = key0 + i0 + u;
+        kr[u] = key < j1 ? *reinterpret_cast<const uint4*>(kb + (long long)key * a.ldkv) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int h = 0; h < kMaxGroup; ++h) {
-        if (h < G) {
+      for (int u = 0; u < U; ++u) {
+        float kf[8];
+        unpack_bf16x8(kr[u], kf);
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
           float d = 0.0f;
 #pragma unroll
-          for (int e = 0; e < E; ++e) d = fmaf(qv[h][e], kf[e], d);
-          d = warp_sum(d);
-          if (lane == j) sc[h] = d;
+          for (int e = 0; e < 8; ++e) d = fmaf(qv[h][e], kf[e], d);
+#pragma unroll
+          for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          if (sl == i0 + u) sc[h] = d;
         }
       }
     }
+    const bool live = blk + lane < j1;
     // ---- block softmax statistics and rescale
-    float p[kMaxGroup];
+    float p[GP];
 #pragma unroll
-    for (int h = 0; h < kMaxGroup; ++h) {
-      if (h < G) {
-        const float bm = warp_max(sc[h]);
-        const float nm = fmaxf(m[h], bm);
-        const float corr = __expf(m[h] - nm);           // 0 on the first block (m = -inf)
-        p[h] = lane < nk ? __expf(sc[h] - nm) : 0.0f;
-        l[h] = l[h] * corr + warp_sum(p[h]);
-        m[h] = nm;
+    for (int h = 0; h < GP; ++h) {
+      const float s = live ? sc[h] : -INFINITY;
+      const float nm = fmaxf(m[h], warp_max(s));
+      const float corr = __expf(m[h] - nm);             // 0 on the first block (m = -inf)
+      p[h] = live ? __expf(s - nm) : 0.0f;
+      l[h] = l[h] * corr + warp_sum(p[h]);
+      m[h] = nm;
 #pragma unroll
-        for (int e = 0; e < E; ++e) acc[h][e] *= corr;
-      } else {
-        p[h] = 0.0f;
-      }
+      for (int e = 0; e < 8; ++e) acc[h][e] *= corr;
     }
-    // ---- P.V: broadcast key j's probabilities, every lane accumulates its dims
-#pragma unroll 4
-    for (int j = 0; j < nk; ++j) {
-      float vf[E];
-      const __nv_bfloat16* vr = vb + (long long)(blk + j) * a.ldkv;
-      if (E == 4) {
-        const uint2 u = *reinterpret_cast<const uint2*>(vr);
-        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-        const float2 p1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-        vf[0] = p0.x; vf[1] = p0.y; vf[E - 2] = p1.x; vf[E - 1] = p1.y;
-      } else {
-        const float2 p0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vr));
-        vf[0] = p0.x; vf[1] = p0.y;
+    // ---- P.V: every sub-group accumulates its own keys; the sub-groups are folded once at the end
+#pragma unroll 1
+    for (int i0 = 0; i0 < LPK; i0 += U) {
+      uint4 vr[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int key = key0 + i0 + u;
+        vr[u] = key < j1 ? *reinterpret_cast<const uint4*>(vb + (long long)key * a.ldkv) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int h = 0; h < kMaxGroup; ++h) {
-        if (h < G) {
-          const float pj = __shfl_sync(0xffffffffu, p[h], j);
+      for (int u = 0; u < U; ++u) {
+        float vf[8];
+        unpack_bf16x8(vr[u], vf);
 #pragma unroll
-          for (int e = 0; e < E; ++e) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
+        for (int h = 0; h < GP; ++h) {
+          const float pj = __shfl_sync(0xffffffffu, p[h], sg0 + i0 + u);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
         }
       }
     }
   }
-  // ---- merge the warps of the CTA (fixed order)
+  // ---- fold the sub-groups of the warp, then the warps of the CTA (fixed order)
 #pragma unroll
-  for (int h = 0; h < kMaxGroup; ++h) {
-    if (h < G) {
-      if (lane == 0) {
-        s_m[warp][h] = m[h];
-        s_l[warp][h] = l[h];
-      }
+  for (int h = 0; h < GP; ++h)
 #pragma unroll
-      for (int e = 0; e < E; ++e) s_acc[warp][h][lane * E + e] = acc[h][e];
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int o = 16; o >= LPK; o >>= 1) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
+#pragma unroll
+  for (int h = 0; h < GP; ++h) {
+    if (lane == 0) {
+      s_m[warp][h] = m[h];
+      s_l[warp][h] = l[h];
+    }
+    if (lane < LPK) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_acc[warp][h][lane * 8 + e] = acc[h][e];
     }
   }
   __syncthreads();
@@ -221,33 +245,36 @@ rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, __nv_bfloat
   __nv_bfloat16* r = qkv + (long long)row * ld;
   const int half = rotary_dim / 2;
   const int heads = Hq + 2 * Hkv;
-  for (int idx = threadIdx.x; idx < heads * (HD / 2); idx += blockDim.x) {
-    const int h = idx / (HD / 2), i = idx % (HD / 2);
-    // pair (i, i + half) inside the rotary part; dims >= rotary_dim pass through (handled as a pair (d0, d1) with
-    // d0 = rotary_dim + 2 * (i - half), d1 = d0 + 1 so that every element is visited exactly once)
-    int d0, d1;
-    bool rot;
-    if (i < half) { d0 = i; d1 = i + half; rot = true; }
-    else { d0 = rotary_dim + 2 * (i - half); d1 = d0 + 1; rot = false; }
+  // Thread -> one pair index i (angle computed once) and a strided subset of the heads.
+  constexpr int PAIRS = HD / 2;
+  const int i = threadIdx.x % PAIRS, hg = threadIdx.x / PAIRS, hstep = blockDim.x / PAIRS;
+  // pair (i, i + half) inside the rotary part; dims >= rotary_dim pass through as the pair
+  // (rotary_dim + 2 (i - half), + 1), so that every element is visited exactly once
+  int d0, d1;
+  float cs = 1.0f, sn = 0.0f;
+  if (i < half) {
+    d0 = i;
+    d1 = i + half;
+    const float inv = powf(base, -2.0f * (float)i / (float)rotary_dim);
+    sincosf((float)pos * inv, &sn, &cs);
+  } else {
+    d0 = rotary_dim + 2 * (i - half);
+    d1 = d0 + 1;
+  }
+  for (int h = hg; h < heads; h += hstep) {
     __nv_bfloat16* src = r + (long long)h * HD;
-    float x0 = __bfloat162float(src[d0]), x1 = __bfloat162float(src[d1]);
+    const float x0 = __bfloat162float(src[d0]), x1 = __bfloat162float(src[d1]);
     const bool is_v = h >= Hq + Hkv;
-    if (rot && !is_v) {
-      const float inv = powf(base, -2.0f * (float)i / (float)rotary_dim);
-      float sn, cs;
-      sincosf((float)pos * inv, &sn, &cs);
-      const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
-      x0 = y0;
-      x1 = y1;
-    }
+    const float y0 = is_v ? x0 : x0 * cs - x1 * sn;
+    const float y1 = is_v ? x1 : x1 * cs + x0 * sn;
     if (h < Hq) {
-      src[d0] = __float2bfloat16(x0);
-      src[d1] = __float2bfloat16(x1);
+      src[d0] = __float2bfloat16(y0);
+      src[d1] = __float2bfloat16(y1);
     } else {
       const int g = is_v ? h - Hq - Hkv : h - Hq;
       __nv_bfloat16* dst = (is_v ? vc : kc) + (long long)b * kv_batch_stride + (long long)pos * ldkv + (long long)g * HD;
-      dst[d0] = __float2bfloat16(x0);
-      dst[d1] = __float2bfloat16(x1);
+      dst[d0] = __float2bfloat16(y0);
+      dst[d1] = __float2bfloat16(y1);
     }
   }
 }
@@ -274,11 +301,11 @@ struct DptbDecodeArgs {
 extern "C" long long dptb_attn_decode_ws_floats(int B, int Sq, int Hq, int head_dim, int splits) {
   return splits <= 1 ? 0 : (long long)B * Sq * Hq * splits * (head_dim + 2);
 }
-// Split count that fills the GPU: about two CTAs per SM, at least 256 keys per CTA.
+// Split count that fills the GPU: about four CTAs per SM, at least 128 keys (one 32-key block per warp) per CTA.
 extern "C" int dptb_attn_decode_splits(int B, int Sq, int Hkv, int Sk) {
   const int base = B * Sq * Hkv;
-  int s = (2 * sm_count() + base - 1) / base;
-  const int cap = (Sk + 255) / 256;
+  int s = (4 * sm_count() + base - 1) / base;
+  const int cap = (Sk + 127) / 128;
   if (s > cap) s = cap;
   if (s > 64) s = 64;
   return s < 1 ? 1 : s;
@@ -289,9 +316,9 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
   if (h->B <= 0 || h->Sq <= 0 || h->Sk <= 0) return 0;
   if (h->Hkv <= 0 || h->Hq % h->Hkv || h->Hq / h->Hkv > kMaxGroup) return kErrUnsupported;
   if (h->head_dim != 64 && h->head_dim != 128) return kErrUnsupported;
-  const int E = h->head_dim / 32;
-  if ((h->ldkv % E) || (h->kv_batch_stride % E) || (reinterpret_cast<uintptr_t>(h->k) & (2 * E - 1)) ||
-      (reinterpret_cast<uintptr_t>(h->v) & (2 * E - 1)))
+  // rows are read in 16-byte pieces
+  if ((h->ldkv % 8) || (h->kv_batch_stride % 8) || (h->ldq % 8) || (reinterpret_cast<uintptr_t>(h->k) & 15) ||
+      (reinterpret_cast<uintptr_t>(h->v) & 15) || (reinterpret_cast<uintptr_t>(h->q) & 15))
     return kErrBadShape;
   DecodeArgs a;
   a.q = static_cast<const __nv_bfloat16*>(h->q);
@@ -307,8 +334,15 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
   if (a.splits > 1 && (!a.ws || h->ws_floats < dptb_attn_decode_ws_floats(a.B, a.Sq, a.Hq, h->head_dim, a.splits)))
     return kErrTooLarge;
   dim3 grid(a.splits, a.Hkv, a.B * a.Sq);
-  if (h->head_dim == 128) attn_decode_kernel<128><<<grid, kDecWarps * 32, 0, st>>>(a);
-  else                    attn_decode_kernel<64><<<grid, kDecWarps * 32, 0, st>>>(a);
+  const int G = a.Hq / a.Hkv;
+  const int gp = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8;
+#define DPTB_DEC(HDV, GPV) attn_decode_kernel<HDV, GPV><<<grid, kDecWarps * 32, 0, st>>>(a)
+  if (h->head_dim == 128) {
+    if (gp == 1) DPTB_DEC(128, 1); else if (gp == 2) DPTB_DEC(128, 2); else if (gp == 4) DPTB_DEC(128, 4); else DPTB_DEC(128, 8);
+  } else {
+    if (gp == 1) DPTB_DEC(64, 1); else if (gp == 2) DPTB_DEC(64, 2); else if (gp == 4) DPTB_DEC(64, 4); else DPTB_DEC(64, 8);
+  }
+#undef DPTB_DEC
   DPTB_CUDA_OK(cudaGetLastError());
   if (a.splits > 1) {
     dim3 mg(a.Hq, a.B * a.Sq);

@@ -38,7 +38,36 @@ tp_argmax_kernel(const TpArgmaxArgs a) {
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   const __nv_bfloat16* row = a.logits + (long long)b * a.ld;
-  for (int i = threadIdx.x; i < a.Vl; i += blockDim.x) {
+  int i0 = 0;
+  if ((a.ld % 8) == 0 && (reinterpret_cast<uintptr_t>(a.logits) & 15) == 0) {
+    // 16-byte loads, four in flight per thread
+    const int nv = a.Vl / 8;
+    for (int v0 = threadIdx.x; v0 < nv; v0 += 4 * blockDim.x) {
+      uint4 u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int vi = v0 + k * blockDim.x;
+        u[k] = vi < nv ? *reinterpret_cast<const uint4*>(row + (long long)vi * 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int vi = v0 + k * blockDim.x;
+        if (vi >= nv) continue;
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = __bfloat162float(e[j]);
+          const int i = vi * 8 + j;
+          if (v > best || (v == best && i < best_i)) {
+            best = v;
+            best_i = i;
+          }
+        }
+      }
+    }
+    i0 = nv * 8;
+  }
+  for (int i = i0 + threadIdx.x; i < a.Vl; i += blockDim.x) {
     const float v = __bfloat162float(row[i]);
     if (v > best || (v == best && i < best_i)) {
       best = v;

@@ -24,10 +24,22 @@ def manual_seed(seed: int) -> None:
     _rng_state["offset"] = 0
 
 
+_grad_listener = None
+
+
+def set_grad_listener(listener) -> None:
+    """``listener.touch(p)`` is called whenever a backward kernel is about to accumulate into ``p``'s arena gradient
+    (data-parallel overlap uses it to learn when a bucket is final)."""
+    global _grad_listener
+    _grad_listener = listener
+
+
 def _direct_grad(p: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """The preallocated gradient buffer of ``p`` if it takes in-kernel accumulation, else None."""
     if p is None or not getattr(p, "_dptb_direct_grad", False):
         return None
+    if _grad_listener is not None:
+        _grad_listener.touch(p)
     return p.grad
 
 

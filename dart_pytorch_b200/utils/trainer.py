@@ -40,6 +40,8 @@ class Trainer:
     def _device_step(self, x, y, split_optimizer: bool):
         self.opt.zero_grad()
         loss = self.loss_fn(self.model, x, y)
+        if self.reducer is not None and hasattr(self.reducer, "begin_step"):
+            self.reducer.begin_step()          # buckets may be reduced under the rest of the backward pass
         loss.backward()
         norm = None
         clipped = False
