@@ -25,15 +25,26 @@ class MoEBlock(Module):
 
     def __init__(self, embed_dim: int, num_heads: int, num_routed_experts: int, num_shared_experts: int, top_k: int,
                  expert_hidden_dim: int, dropout_p: float = 0.0, device=None, seed: int = 0, norm: str = "layer",
-                 rope: Optional[RopeCache] = None, dtype=torch.float32, init_std: Optional[float] = None, **moe_kw):
+                 rope: Optional[RopeCache] = None, dtype=torch.float32, init_std: Optional[float] = None,
+                 ep_group=None, **moe_kw):
         super().__init__()
         mk_norm = (lambda: RMSNorm(embed_dim, device=device, dtype=dtype)) if norm == "rms" else \
             (lambda: LayerNorm(embed_dim, device=device, dtype=dtype))
         self.ln1, self.ln2 = mk_norm(), mk_norm()
         self.attn = MultiHeadAttention(embed_dim, num_heads, dropout_p=dropout_p, device=device, seed=seed, rope=rope,
                                        dtype=dtype, init_std=init_std)
-        self.moe = MoEFeedForward(embed_dim, num_routed_experts, num_shared_experts, top_k, expert_hidden_dim,
-                                  device=device, seed=seed + 4000, dtype=dtype, init_std=init_std, **moe_kw)
+        if ep_group is not None:
+            # experts sharded over the ranks of `ep_group`: SwiGLU experts, softmax top-k, per-source capacity quota
+            from ..parallel.ep import ExpertParallelMoE
+            self.moe = ExpertParallelMoE(embed_dim, expert_hidden_dim, num_routed_experts, top_k=top_k,
+                                         capacity_factor=moe_kw.get("capacity_factor") or 1.25,
+                                         aux_loss_coef=moe_kw.get("aux_loss_coef", 0.0), group=ep_group,
+                                         renormalize_top_k=bool(moe_kw.get("renormalize_top_k")),
+                                         route_scale=moe_kw.get("route_scale", 1.0), device=device, seed=seed + 4000,
+                                         dtype=dtype, init_std=init_std)
+        else:
+            self.moe = MoEFeedForward(embed_dim, num_routed_experts, num_shared_experts, top_k, expert_hidden_dim,
+                                      device=device, seed=seed + 4000, dtype=dtype, init_std=init_std, **moe_kw)
         self.dropout = Dropout(dropout_p)
 
     def submodules(self):
@@ -55,8 +66,9 @@ class MoELanguageModel(Module):
                  top_k_groups: Optional[int] = None, route_scale: float = 1.0, sparse_execution: bool = False,
                  renormalize_top_k: Optional[bool] = None, norm: str = "layer", rope_base: Optional[float] = None,
                  capacity_factor: Optional[float] = None, aux_loss_coef: float = 0.0, expert_bias: bool = True,
-                 head_bias: bool = True, dtype=torch.float32, init_std: Optional[float] = None):
+                 head_bias: bool = True, dtype=torch.float32, init_std: Optional[float] = None, ep_group=None):
         super().__init__()
+        self.ep_group = ep_group
         self.vocab_size, self.embed_dim, self.num_layers, self.num_heads = vocab_size, embed_dim, num_layers, num_heads
         self.max_len = max_len
         self.token_emb = Embedding(vocab_size, embed_dim, device=device, seed=seed, dtype=dtype, init_std=init_std)
@@ -70,7 +82,8 @@ class MoELanguageModel(Module):
                      expert_variant=expert_variant, gate_function=gate_function, bias_update_rule=bias_update_rule,
                      num_expert_groups=num_expert_groups, top_k_groups=top_k_groups, route_scale=route_scale,
                      sparse_execution=sparse_execution, renormalize_top_k=renormalize_top_k,
-                     capacity_factor=capacity_factor, aux_loss_coef=aux_loss_coef, expert_bias=expert_bias)
+                     capacity_factor=capacity_factor, aux_loss_coef=aux_loss_coef, expert_bias=expert_bias,
+                     ep_group=ep_group)
             for i in range(num_layers)]
         self.final_ln = RMSNorm(embed_dim, device=device, dtype=dtype) if norm == "rms" else \
             LayerNorm(embed_dim, device=device, dtype=dtype)
@@ -113,6 +126,14 @@ class MoELanguageModel(Module):
         ce = F.mean(F.cross_entropy(logits.reshape(-1, self.vocab_size), targets.reshape(-1))).reshape(())
         aux = self.aux_loss()
         return ce if aux is None else ce + aux.to(ce.dtype)
+
+    def expert_parameters(self):
+        """Parameters that live on one rank only (expert-parallel shards); data-parallel reduction must skip them."""
+        out = []
+        for b in self.blocks:
+            if hasattr(b.moe, "expert_parameters"):
+                out.extend(b.moe.expert_parameters())
+        return out
 
     def update_routing_bias(self) -> None:
         for b in self.blocks:

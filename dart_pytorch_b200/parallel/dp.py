@@ -25,12 +25,16 @@ import torch.distributed as dist
 
 class GradReducer:
     def __init__(self, arena, world_size: int, mode: str = "auto", bucket_mb: float = 32.0, group=None,
-                 overlap: bool = False):
+                 overlap: bool = False, exclude=()):
+        """``exclude``: parameters that exist on this rank only (expert-parallel shards).  Their gradients are not
+        averaged; their squared norm is summed over the ranks and folded into the global gradient norm."""
         self.arena, self.world = arena, world_size
         self.group = group
         self.mode = mode
         self.bucket_elems = int(bucket_mb * 1024 * 1024 / arena.grad.element_size())
-        self.buckets = arena.slices(self.bucket_elems)
+        self.exclude = list(exclude)
+        self.buckets = arena.slices(self.bucket_elems, exclude=self.exclude)
+        self.local_ranges = arena.ranges_of(self.exclude) if self.exclude else []
         self.impl = None
         if mode in ("auto", "fused"):
             try:
@@ -107,6 +111,26 @@ class GradReducer:
                 self._launch(b)
         torch.cuda.current_stream().wait_stream(self._side)
 
+    def _fold_local_norm(self, ctrl: torch.Tensor, max_norm: float) -> None:
+        """ctrl = {norm, scale, finite, sumsq} of the averaged ranges; add the ranks' own squared norms of the
+        rank-local ranges (one tiny sum over the group) and recompute norm and clip scale on the device."""
+        g = self.arena.grad
+        local = torch.zeros(1, dtype=torch.float32, device=g.device)
+        for s, e in self.local_ranges:
+            # a rank-local expert already holds the summed contributions of every rank's tokens; the global loss is
+            # the mean of the ranks' losses, so it takes the same 1 / world factor as the averaged ranges
+            g[s:e].mul_(1.0 / self.world)
+            local += g[s:e].float().pow(2).sum()
+        dist.all_reduce(local, op=dist.ReduceOp.SUM, group=self.group)
+        total = ctrl[3] + local[0]
+        norm = total.sqrt()
+        ctrl[3] = total
+        ctrl[0] = norm
+        finite = torch.isfinite(norm)
+        ctrl[2] = finite.float()
+        if max_norm > 0.0:
+            ctrl[1] = torch.where(finite & (norm > max_norm), max_norm / norm, torch.ones_like(norm))
+
     # ---- reduction --------------------------------------------------------------------------------------
     def reduce(self, ctrl: Optional[torch.Tensor] = None, max_norm: float = 0.0) -> bool:
         """Average ``arena.grad`` across ranks (called after backward, before the optimizer).
@@ -128,6 +152,8 @@ class GradReducer:
                 self.impl.finalize(ctrl, 0.0)
                 return False
             self.impl.finalize(ctrl, max_norm)
+            if self.local_ranges:
+                self._fold_local_norm(ctrl, max_norm)
             return True
         g = self.arena.grad
         for (s, e) in self.buckets:

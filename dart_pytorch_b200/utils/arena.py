@@ -77,15 +77,36 @@ class ParamArena:
         if self.master is not None:
             self.flat.copy_(self.master.to(self.dtype))
 
-    def slices(self, bucket_elems: int):
-        """Contiguous ``(start, end)`` ranges of about ``bucket_elems`` elements that respect parameter boundaries."""
+    def slices(self, bucket_elems: int, exclude=()):
+        """Contiguous ``(start, end)`` ranges of about ``bucket_elems`` elements that respect parameter boundaries.
+        Parameters in ``exclude`` (compared by identity) are left out: a range ends before one and the next starts
+        after it."""
+        skip = {id(p) for p in exclude}
         out, start, cur = [], 0, 0
         for p in self.ordered:
             n = (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+            if id(p) in skip:
+                if cur > start:
+                    out.append((start, cur))
+                cur += n
+                start = cur
+                continue
             cur += n
             if cur - start >= bucket_elems:
                 out.append((start, cur))
                 start = cur
         if cur > start:
             out.append((start, cur))
+        return out
+
+    def ranges_of(self, params):
+        """Merged ``(start, end)`` element ranges covered by ``params``."""
+        spans = sorted((self.offsets[id(p)], self.offsets[id(p)] + (p.numel() + ALIGN - 1) // ALIGN * ALIGN)
+                       for p in params)
+        out = []
+        for s, e in spans:
+            if out and out[-1][1] == s:
+                out[-1] = (out[-1][0], e)
+            else:
+                out.append((s, e))
         return out

@@ -281,3 +281,59 @@ def test_tensor_facade_contract():
     assert ce.shape == [2, 1]
     lin = nn.Linear(3, 2)
     assert isinstance(lin(logits), T)
+
+
+def test_train_state_sidecar_resumes_exactly(tmp_path):
+    """Parameters (DPTC) + sidecar (optimizer moments, step, scheduler, RNG) reproduce an uninterrupted run."""
+    import random
+    from dart_pytorch_b200.io.dptc import Checkpoint
+    from dart_pytorch_b200.io.train_state import load_train_state, save_train_state
+    from dart_pytorch_b200.models import GPT, GPTConfig
+    import dart_pytorch_b200 as dp
+
+    def make():
+        m = GPT(GPTConfig(vocab_size=31, max_ctx=12, embed_dim=16, num_layers=1, num_heads=2, seed=4))
+        o = dp.Adam(m.parameters(), lr=1e-2, weight_decay=0.05)
+        s = dp.LinearWarmupCosineDecay(o, warmup_steps=3, total_steps=20, max_lr=1e-2, min_lr=1e-3)
+        return m, o, s
+
+    def run(m, o, s, steps, g):
+        for _ in range(steps):
+            x = torch.randint(0, 31, (2, 12), generator=g)
+            o.zero_grad()
+            m.loss(x[:, :-1], x[:, 1:]).backward()
+            o.step()
+            s.step()
+    g = torch.Generator().manual_seed(0)
+    m1, o1, s1 = make()
+    run(m1, o1, s1, 4, g)
+    Checkpoint.save_file(m1, str(tmp_path / "m.dptc"))
+    save_train_state(str(tmp_path / "m.dpts"), o1, s1, extra={"tokens_seen": 96})
+    gstate = g.get_state()
+    random.seed(123)
+    torch.manual_seed(77)
+    save_train_state(str(tmp_path / "rng.dpts"))
+    want_py, want_t = random.random(), torch.rand(3)
+    run(m1, o1, s1, 3, g)
+    m2, o2, s2 = make()
+    Checkpoint.load_into_file(m2, str(tmp_path / "m.dptc"))
+    extra = load_train_state(str(tmp_path / "m.dpts"), o2, s2, restore_rng=False)
+    assert extra == {"tokens_seen": 96} and o2._step == 4 and s2.step_count == 4 and abs(o2.lr - o1.lr) > 0
+    g2 = torch.Generator()
+    g2.set_state(gstate)
+    run(m2, o2, s2, 3, g2)
+    for a, b in zip(m1.parameters(), m2.parameters()):
+        assert torch.allclose(a, b, atol=1e-6)
+    assert abs(o1.lr - o2.lr) < 1e-12
+    load_train_state(str(tmp_path / "rng.dpts"))
+    assert random.random() == want_py and torch.equal(torch.rand(3), want_t)
+    blob = (tmp_path / "m.dpts").read_bytes()
+    (tmp_path / "bad.dpts").write_bytes(b"XXXX" + blob[4:])
+    with pytest.raises(ValueError):
+        load_train_state(str(tmp_path / "bad.dpts"), o2, s2)
+    (tmp_path / "short.dpts").write_bytes(blob[:len(blob) - 10])
+    with pytest.raises(ValueError):
+        load_train_state(str(tmp_path / "short.dpts"), o2, s2)
+    sgd = dp.SGD(m2.parameters(), lr=0.1)
+    with pytest.raises(ValueError):
+        load_train_state(str(tmp_path / "m.dpts"), sgd)

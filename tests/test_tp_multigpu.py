@@ -33,3 +33,9 @@ def test_fused_gemm_allreduce_auto_multimem():
 @pytest.mark.parametrize("hd", ["64", "128"])
 def test_tp_llama_engine_matches_whole_model(hd):
     _run("tp_llama_worker.py", hd, port=29545 + (hd == "128"), ok="tp_llama_worker ok")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("cf", ["1.25", "0.5"])
+def test_expert_parallel_moe_matches_dense_reference(cf):
+    _run("ep_worker.py", cf, port=29551 + (cf == "0.5"), ok="ep_worker ok")
