@@ -10,12 +10,15 @@
 // Grouped-query attention: query head h reads KV head h / (Hq / Hkv).
 //
 // One CTA owns NQ query tiles of 128 rows of one (batch, head) and walks the KV sequence in tiles of 128 keys:
-//   warps 0-3 / 4-7  softmax warpgroups, one per query tile, one thread per query row: read S from TMEM, online
-//                    max / sum, write P (bf16) into shared memory in the tensor core's K-major swizzled layout, and
-//                    fold the per-tile P.V results (read back from TMEM) into register accumulators
-//   warp 8           TMA producer (Q once, K / V through a 2-stage ring)
-//   warp 9           MMA issuer: S_t = Q_t K_j^T and O_t = P_t V_j, interleaved over the query tiles so one
-//                    warpgroup's softmax overlaps the other's matrix products
+//   warps 0-3 / 4-7  softmax warpgroups, one per query tile, one thread per query row: pull the whole S row (128
+//                    scores) from TMEM into registers in one go and hand the S columns straight back to the tensor
+//                    core, so S_t(j+1) = Q_t K_{j+1}^T is computed while this tile's softmax runs; then max / exp2 /
+//                    sum and P (bf16) into shared memory in the tensor core's K-major swizzled layout
+//   warp 8           TMA producer (Q once, K / V through rings)
+//   warp 9           MMA issuer: S_t = Q_t K_j^T, and O_t += P_t V_j accumulated in TMEM
+// The output accumulator never leaves TMEM during the loop.  The running maximum is lazy: a row keeps exponentiating
+// against an older maximum until the true one has grown by more than 8 (a factor 256 of headroom in fp32 / bf16);
+// only then (decided per warp) O is pulled out, rescaled and stored back, which after the first tiles is rare.
 #include <cuda_bf16.h>
 
 #include "common/host.h"
@@ -42,28 +45,34 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 constexpr int kAttnBM = 128;   // query rows per tile
 constexpr int kAttnBN = 128;   // keys per tile
-constexpr int kAttnStages = 2;
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;   // two softmax warpgroups + one warpgroup holding the TMA and MMA warps
+// Registers per thread after the hand-over.  The CTA starts with 384 x 168 registers and the pool does not grow:
+// 2 x 128 x 216 + 128 x 72 = 384 x 168, so the increase can always be satisfied once the producers have shrunk.
+constexpr int kSoftmaxRegs = 216;
+constexpr int kProducerRegs = 72;
+static_assert(2 * 128 * kSoftmaxRegs + 128 * kProducerRegs <= kAttnThreads * 168, "register hand-over must balance");
+constexpr float kLazyMaxSlack = 8.0f;   // log2 units a row's maximum may grow before O is rescaled
 
-template <int HD, int NQ>
+template <int HD, int NQ, int KST, int VST>
 struct AttnFwdSmem {
   static constexpr int kQBytes = kAttnBM * HD * 2;
   static constexpr int kKVBytes = kAttnBN * HD * 2;
   static constexpr int kPBytes = kAttnBM * kAttnBN * 2;
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + NQ * kQBytes;
-  static constexpr int kVOff = kKOff + kAttnStages * kKVBytes;
-  static constexpr int kPOff = kVOff + kAttnStages * kKVBytes;
+  static constexpr int kVOff = kKOff + KST * kKVBytes;
+  static constexpr int kPOff = kVOff + VST * kKVBytes;
   static constexpr int kBarOff = kPOff + NQ * kPBytes;
-  static constexpr int kNumBars = NQ + 4 * kAttnStages + 4 * NQ + 1;
+  static constexpr int kNumBars = NQ + 2 * KST + 2 * VST + 4 * NQ + 1;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16 + 1024;
+  static_assert(kTotal <= 227 * 1024, "attention forward: shared memory budget");
 };
 
-template <int HD, int NQ>
+template <int HD, int NQ, int KST, int VST>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
-  using L = AttnFwdSmem<HD, NQ>;
+  using L = AttnFwdSmem<HD, NQ, KST, VST>;
   constexpr int kChunks = HD / 64;            // 64-column (128-byte) chunks per head row
   constexpr int TMEM_COLS = 512;
   constexpr int kSCol = 0;                    // S_t at columns [t*128, t*128+128)
@@ -72,15 +81,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* q_full = bars;                          // [NQ]
-  uint64_t* k_full = q_full + NQ;                   // [stages]
-  uint64_t* v_full = k_full + kAttnStages;
-  uint64_t* k_empty = v_full + kAttnStages;
-  uint64_t* v_empty = k_empty + kAttnStages;
-  uint64_t* s_full = v_empty + kAttnStages;         // [NQ]
-  uint64_t* p_full = s_full + NQ;
-  uint64_t* o_full = p_full + NQ;
-  uint64_t* o_empty = o_full + NQ;
-  uint64_t* drain_bar = o_empty + NQ;
+  uint64_t* k_full = q_full + NQ;                   // [KST]
+  uint64_t* k_empty = k_full + KST;
+  uint64_t* v_full = k_empty + KST;                 // [VST]
+  uint64_t* v_empty = v_full + VST;
+  uint64_t* s_full = v_empty + VST;                 // [NQ] S_t(j) is in TMEM
+  uint64_t* s_empty = s_full + NQ;                  // [NQ] S_t(j) has been copied to registers
+  uint64_t* p_full = s_empty + NQ;                  // [NQ] P_t(j) is in shared memory (and O_t is rescaled)
+  uint64_t* o_full = p_full + NQ;                   // [NQ] O_t += P_t(j) V_j has completed
+  uint64_t* drain_bar = o_full + NQ;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -121,14 +130,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int t = 0; t < NQ; ++t) {
         mbar_init(&q_full[t], 1);
         mbar_init(&s_full[t], 1);
+        mbar_init(&s_empty[t], kAttnBM);
         mbar_init(&p_full[t], kAttnBM);
         mbar_init(&o_full[t], 1);
-        mbar_init(&o_empty[t], kAttnBM);
       }
-      for (int s = 0; s < kAttnStages; ++s) {
+      for (int s = 0; s < KST; ++s) {
         mbar_init(&k_full[s], 1);
-        mbar_init(&v_full[s], 1);
         mbar_init(&k_empty[s], 1);
+      }
+      for (int s = 0; s < VST; ++s) {
+        mbar_init(&v_full[s], 1);
         mbar_init(&v_empty[s], 1);
       }
       mbar_init(drain_bar, 1);
@@ -142,6 +153,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  static_assert(NQ == 2, "warp roles assume two softmax warpgroups");
+  if (warp >= 8) {
+    warpgroup_reg_dec<kProducerRegs>();
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -152,33 +166,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tma_load_3d(smem + L::kQOff + t * L::kQBytes + c * (kAttnBM * 128), &tmQ, &q_full[t], head * HD + c * 64,
                       q_row0 + t * kAttnBM, batch);
       }
-      int issued = 0;
+      int k_issued = 0, v_issued = 0;
       for (int j = 0; j < n_max; ++j) {
-        const int s = j % kAttnStages;
-        const uint32_t ph = (j / kAttnStages) & 1;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) break;
-        mbar_arrive_expect_tx(&k_full[s], L::kKVBytes);
+        const int ks = j % KST, vs = j % VST;
+        if (!mbar_wait(&k_empty[ks], ((j / KST) & 1) ^ 1, abort_flag, kWaitEmptyTimeout)) break;
+        mbar_arrive_expect_tx(&k_full[ks], L::kKVBytes);
         for (int c = 0; c < kChunks; ++c)
-          tma_load_3d(smem + L::kKOff + s * L::kKVBytes + c * (kAttnBN * 128), &tmK, &k_full[s], kv_head * HD + c * 64,
-                      j * kAttnBN, batch);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) { issued = j + 1; break; }
-        mbar_arrive_expect_tx(&v_full[s], L::kKVBytes);
+          tma_load_3d(smem + L::kKOff + ks * L::kKVBytes + c * (kAttnBN * 128), &tmK, &k_full[ks],
+                      kv_head * HD + c * 64, j * kAttnBN, batch);
+        k_issued = j + 1;
+        if (!mbar_wait(&v_empty[vs], ((j / VST) & 1) ^ 1, abort_flag, kWaitEmptyTimeout)) break;
+        mbar_arrive_expect_tx(&v_full[vs], L::kKVBytes);
         for (int c = 0; c < kChunks; ++c)
-          tma_load_3d(smem + L::kVOff + s * L::kKVBytes + c * (kAttnBN * 128), &tmV, &v_full[s], kv_head * HD + c * 64,
-                      j * kAttnBN, batch);
-        issued = j + 1;
+          tma_load_3d(smem + L::kVOff + vs * L::kKVBytes + c * (kAttnBN * 128), &tmV, &v_full[vs],
+                      kv_head * HD + c * 64, j * kAttnBN, batch);
+        v_issued = j + 1;
       }
       if (*abort_flag) {
         // Wait (bounded) for copies that may still be landing in this CTA's shared memory.
         const uint64_t t0 = global_timer_ns();
         for (int t = 0; t < NQ; ++t)
           while (n_tiles[t] && !mbar_try_wait(&q_full[t], 0) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
-        for (int j = max(0, issued - kAttnStages); j < issued; ++j) {
-          const int s = j % kAttnStages;
-          const uint32_t ph = (j / kAttnStages) & 1;
-          while (!mbar_try_wait(&k_full[s], ph) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
-          while (!mbar_try_wait(&v_full[s], ph) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
-        }
+        for (int j = max(0, k_issued - KST); j < k_issued; ++j)
+          while (!mbar_try_wait(&k_full[j % KST], (j / KST) & 1) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
+        for (int j = max(0, v_issued - VST); j < v_issued; ++j)
+          while (!mbar_try_wait(&v_full[j % VST], (j / VST) & 1) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
       }
     }
   } else if (warp == 9) {
@@ -189,9 +201,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool issued_any = false;
       bool ok = true;
       auto issue_s = [&](int t, int j) {
-        const int s = j % kAttnStages;
         const uint32_t qa = smem_u32(smem + L::kQOff + t * L::kQBytes);
-        const uint32_t kb = smem_u32(smem + L::kKOff + s * L::kKVBytes);
+        const uint32_t kb = smem_u32(smem + L::kKOff + (j % KST) * L::kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk / 4) * (kAttnBM * 128) + (kk % 4) * 32;
@@ -214,42 +225,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (ok) umma_commit(&k_empty[0]);
       }
       for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j % kAttnStages;
-        const uint32_t ph = (j / kAttnStages) & 1;
-        ok = mbar_wait(&v_full[s], ph, abort_flag, kWaitFullTimeout);
-        bool next_k_waited = false;
-        for (int t = 0; t < NQ && ok; ++t) {
-          if (j < n_tiles[t]) {
-            // P_t(j) is in shared memory (and S_t has been read); O_t of the previous tile has been consumed.
-            ok = mbar_wait(&p_full[t], j & 1, abort_flag, kWaitFlagTimeout);
-            if (ok && j > 0) ok = mbar_wait(&o_empty[t], (j - 1) & 1, abort_flag, kWaitFlagTimeout);
+        // (a) S_t(j+1) as soon as the softmax warpgroup has copied S_t(j) out of TMEM.
+        if (j + 1 < n_max) {
+          const int ks1 = (j + 1) % KST;
+          ok = mbar_wait(&k_full[ks1], ((j + 1) / KST) & 1, abort_flag, kWaitFullTimeout);
+          for (int t = 0; t < NQ && ok; ++t) {
+            if (j + 1 >= n_tiles[t]) continue;
+            ok = mbar_wait(&s_empty[t], j & 1, abort_flag, kWaitTmemEmptyTimeout);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t pa = smem_u32(smem + L::kPOff + t * L::kPBytes);
-            const uint32_t vb = smem_u32(smem + L::kVOff + s * L::kKVBytes);
-#pragma unroll
-            for (int kk = 0; kk < kAttnBN / 16; ++kk) {
-              const uint32_t aoff = (kk / 4) * (kAttnBM * 128) + (kk % 4) * 32;
-              umma_bf16(tmem_base + kOCol + t * HD, make_smem_desc(pa + aoff, 16, 1024),
-                        make_smem_desc(vb + kk * 2048, kAttnBN * 128, 1024), idesc_o, kk != 0);
-            }
-            umma_commit(&o_full[t]);
-            issued_any = true;
-          }
-          if (j + 1 < n_tiles[t]) {
-            const int s1 = (j + 1) % kAttnStages;
-            if (!next_k_waited) {
-              ok = mbar_wait(&k_full[s1], ((j + 1) / kAttnStages) & 1, abort_flag, kWaitFullTimeout);
-              if (!ok) break;
-              next_k_waited = true;
-              tc_fence_after_sync();
-            }
             issue_s(t, j + 1);
           }
+          if (!ok) break;
+          umma_commit(&k_empty[ks1]);
+        }
+        // (b) O_t += P_t(j) V_j once P_t(j) is in shared memory.
+        const int vs = j % VST;
+        ok = mbar_wait(&v_full[vs], (j / VST) & 1, abort_flag, kWaitFullTimeout);
+        for (int t = 0; t < NQ && ok; ++t) {
+          if (j >= n_tiles[t]) continue;
+          ok = mbar_wait(&p_full[t], j & 1, abort_flag, kWaitFlagTimeout);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t pa = smem_u32(smem + L::kPOff + t * L::kPBytes);
+          const uint32_t vb = smem_u32(smem + L::kVOff + vs * L::kKVBytes);
+#pragma unroll
+          for (int kk = 0; kk < kAttnBN / 16; ++kk) {
+            const uint32_t aoff = (kk / 4) * (kAttnBM * 128) + (kk % 4) * 32;
+            umma_bf16(tmem_base + kOCol + t * HD, make_smem_desc(pa + aoff, 16, 1024),
+                      make_smem_desc(vb + kk * 2048, kAttnBN * 128, 1024), idesc_o, (j != 0 || kk != 0) ? 1u : 0u);
+          }
+          umma_commit(&o_full[t]);
+          issued_any = true;
         }
         if (!ok) break;
-        umma_commit(&v_empty[s]);
-        if (next_k_waited) umma_commit(&k_empty[(j + 1) % kAttnStages]);
+        umma_commit(&v_empty[vs]);
       }
       if (*abort_flag && issued_any) {
         umma_commit(drain_bar);
@@ -257,8 +267,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
       }
     }
-  } else if (warp < 4 * NQ) {
+  }
+  } else {
     // ------------------------------------------------------------------ softmax warpgroups
+    warpgroup_reg_inc<kSoftmaxRegs>();
     const int t = warp >> 2;
     const int q = warp & 3;
     const int row_in_tile = q * 32 + lane;
@@ -269,10 +281,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t o_addr = lane_addr + kOCol + t * HD;
     uint8_t* p_tile = smem + L::kPOff + t * L::kPBytes;
 
-    float acc[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) acc[d] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
+    float m_use = -INFINITY;   // the maximum the stored exponentials are relative to (lags the true maximum)
+    float l_run = 0.0f;
     const int key_limit = p.causal ? min(p.Sk - 1, q_row + p.q_offset) : p.Sk - 1;  // last visible key of this row
     bool ok = true;
 
@@ -280,59 +290,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, kWaitTmemFullTimeout));
       if (!ok) break;
       tc_fence_after_sync();
-      const int key0 = j * kAttnBN;
-      const bool need_mask = key0 + kAttnBN - 1 > key_limit;  // per-thread; the branches below stay convergent
-      // Pass 1: row maximum of the raw scores.
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kAttnBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      uint32_t s[kAttnBN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (need_mask && key0 + c * 32 + i > key_limit) v = -INFINITY;
-          mx = fmaxf(mx, v);
-        }
+      for (int c = 0; c < kAttnBN / 32; ++c) tmem_ld_32x32(s_addr + c * 32, reinterpret_cast<uint32_t(&)[32]>(s[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&s_empty[t]);   // the tensor core may overwrite S_t with the next tile's scores
+
+      const int key0 = j * kAttnBN;
+      if (key0 + kAttnBN - 1 > key_limit) {   // per-thread; no warp-level operation inside
+#pragma unroll
+        for (int i = 0; i < kAttnBN; ++i)
+          if (key0 + i > key_limit) s[i] = 0xff800000u;   // -inf
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-      const float alpha = fast_exp2(m_run - m_use);   // m_run = -inf -> 0
-      // Fold in the previous tile's P.V (relative to the previous maximum), then rescale to the new maximum.
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kAttnBN; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      // Lazy maximum: move it only when some row of this warp outgrew its old one by more than the slack (the first
+      // finite tile always does: -inf + slack = -inf).  Rows that move rescale what they have accumulated so far.
+      if (__any_sync(0xffffffffu, m_tile > m_use + kLazyMaxSlack)) {
+        const float m_new = fmaxf(m_use, m_tile);
+        const float alpha = (m_new == -INFINITY) ? 1.0f : fast_exp2(m_use - m_new);   // m_use = -inf -> 0
+        if (j > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, abort_flag, kWaitTmemFullTimeout));
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(o_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+        l_run *= alpha;
+        m_use = m_new;
+      }
+      const float m_sub = (m_use == -INFINITY) ? 0.0f : m_use;
+      // The previous P_t must have been consumed before it is overwritten (it nearly always has been by now).
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, abort_flag, kWaitTmemFullTimeout));
         if (!ok) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(o_addr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = (acc[c * 32 + i] + __uint_as_float(r[i])) * alpha;
-        }
-        tc_fence_before_sync();
-        mbar_arrive(&o_empty[t]);
       }
-      // Pass 2: probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle), row sum.
-      float l_tile = 0.0f;
-#pragma unroll 1
+      // Probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle), row sum.
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+#pragma unroll
       for (int c = 0; c < kAttnBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_ld_wait();
         uint32_t packed[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float a = fast_exp2(__uint_as_float(r[i]) * p.scale_log2 - m_use);
-          float b = fast_exp2(__uint_as_float(r[i + 1]) * p.scale_log2 - m_use);
-          if (need_mask) {
-            if (key0 + c * 32 + i > key_limit) a = 0.0f;
-            if (key0 + c * 32 + i + 1 > key_limit) b = 0.0f;
-          }
-          l_tile += a + b;
-          packed[i >> 1] = pack_bf16x2(a, b);
+        for (int i = 0; i < 32; i += 4) {
+          const float a = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 0]), p.scale_log2, -m_sub));
+          const float b = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), p.scale_log2, -m_sub));
+          const float e = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 2]), p.scale_log2, -m_sub));
+          const float f = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 3]), p.scale_log2, -m_sub));
+          l0 += a; l1 += b; l2 += e; l3 += f;
+          packed[(i >> 1) + 0] = pack_bf16x2(a, b);
+          packed[(i >> 1) + 1] = pack_bf16x2(e, f);
         }
         // 32 keys = 64 bytes = four 16-byte chunks of this row, in 64-key block (c / 2), at chunk (c % 2) * 4 + i.
         uint8_t* blk = p_tile + (c >> 1) * (kAttnBM * 128);
@@ -343,8 +365,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               make_uint4(packed[i * 4 + 0], packed[i * 4 + 1], packed[i * 4 + 2], packed[i * 4 + 3]);
         }
       }
-      l_run = l_run * alpha + l_tile;
-      m_run = m_new;
+      l_run += (l0 + l1) + (l2 + l3);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&p_full[t]);
@@ -353,32 +374,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n - 1) & 1, abort_flag, kWaitTmemFullTimeout));
       if (ok) {
         tc_fence_after_sync();
+        const bool live = q_row < p.Sq;
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        __nv_bfloat16* dst = p.o + ((long long)batch * p.Sq + (live ? q_row : 0)) * p.ldo + (long long)head * HD;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(o_addr + c * 32, r);
           tmem_ld_wait();
+          if (live) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] += __uint_as_float(r[i]);
+            for (int d = 0; d < 32; d += 8) {
+              uint4 u;
+              u.x = pack_bf16x2(__uint_as_float(r[d + 0]) * inv, __uint_as_float(r[d + 1]) * inv);
+              u.y = pack_bf16x2(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
+              u.z = pack_bf16x2(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv);
+              u.w = pack_bf16x2(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + d) = u;
+            }
+          }
         }
         tc_fence_before_sync();
-      }
-    }
-    if (ok && q_row < p.Sq) {
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      __nv_bfloat16* dst = p.o + ((long long)batch * p.Sq + q_row) * p.ldo + (long long)head * HD;
-#pragma unroll
-      for (int d = 0; d < HD; d += 8) {
-        uint4 u;
-        u.x = pack_bf16x2(acc[d + 0] * inv, acc[d + 1] * inv);
-        u.y = pack_bf16x2(acc[d + 2] * inv, acc[d + 3] * inv);
-        u.z = pack_bf16x2(acc[d + 4] * inv, acc[d + 5] * inv);
-        u.w = pack_bf16x2(acc[d + 6] * inv, acc[d + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + d) = u;
-      }
-      if (p.lse) {
-        const float lse2 = (l_run > 0.0f) ? m_run + log2f(l_run) : -INFINITY;
-        p.lse[((long long)batch * p.Hq + head) * p.Sq + q_row] = lse2 * 0.6931471805599453f;
+        if (live && p.lse) {
+          const float lse2 = (l_run > 0.0f) ? m_use + log2f(l_run) : -INFINITY;
+          p.lse[((long long)batch * p.Hq + head) * p.Sq + q_row] = lse2 * 0.6931471805599453f;
+        }
       }
     }
   }
@@ -418,9 +438,9 @@ struct DptbAttnFwdArgs {
   long long kv_batch_rows;  // rows between consecutive batches of K / V (a cache's capacity); 0 = Sk
 };
 
-template <int HD, int NQ>
+template <int HD, int NQ, int KST, int VST>
 static int attn_fwd_launch(const DptbAttnFwdArgs* a, cudaStream_t st) {
-  using L = AttnFwdSmem<HD, NQ>;
+  using L = AttnFwdSmem<HD, NQ, KST, VST>;
   CUtensorMap tmQ, tmK, tmV;
   int rc = encode_tmap_seq(&tmQ, a->q, a->Hq, HD, a->Sq, a->B, a->ldq, kAttnBM);
   if (rc) return rc;
@@ -437,7 +457,7 @@ static int attn_fwd_launch(const DptbAttnFwdArgs* a, cudaStream_t st) {
   p.q_offset = a->q_offset;
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.num_q_blocks = (a->Sq + NQ * kAttnBM - 1) / (NQ * kAttnBM);
-  auto kern = attn_fwd_kernel<HD, NQ>;
+  auto kern = attn_fwd_kernel<HD, NQ, KST, VST>;
   DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
   dim3 grid(p.num_q_blocks, a->Hq, a->B);
   kern<<<grid, kAttnThreads, L::kTotal, st>>>(tmQ, tmK, tmV, p);
@@ -450,7 +470,7 @@ extern "C" int dptb_attn_fwd(const DptbAttnFwdArgs* a, void* stream) {
   if (a->Sk <= 0 || a->Hkv <= 0 || a->Hq % a->Hkv) return kErrBadShape;
   if ((a->ldq % 8) || (a->ldk % 8) || (a->ldv % 8) || (a->ldo % 8)) return kErrBadShape;
   if ((reinterpret_cast<uintptr_t>(a->o) & 15) != 0) return kErrBadShape;
-  if (a->head_dim == 64) return attn_fwd_launch<64, 2>(a, st);
-  if (a->head_dim == 128) return attn_fwd_launch<128, 1>(a, st);
+  if (a->head_dim == 64) return attn_fwd_launch<64, 2, 2, 2>(a, st);
+  if (a->head_dim == 128) return attn_fwd_launch<128, 2, 2, 1>(a, st);
   return kErrUnsupported;
 }

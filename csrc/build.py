@@ -1,8 +1,9 @@
 """Build the native library ``dart_pytorch_b200/_C/libdptb200.so`` for sm_100a with nvcc.
 
-Every ``csrc/*.cu`` file is compiled to an object in parallel (relocatable device code, because the device
-status word is shared between translation units) and linked into one shared library.  Objects are
-rebuilt only when their source or a header under ``csrc/common`` is newer.
+Every ``csrc/*.cu`` file is compiled to an object in parallel (whole-program device code per file: no device
+linking, so the compiler can allocate registers per warp-specialised branch; the device status word is one block per
+translation unit, folded on the host) and linked into one shared library.  Objects are rebuilt only when their source
+or a header under ``csrc/common`` is newer.
 
     python csrc/build.py [--force] [--verbose]
 """
@@ -23,7 +24,7 @@ LIB = OUT_DIR / "libdptb200.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", "-rdc=true",
+    "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
     f"-I{CSRC}",
 ]

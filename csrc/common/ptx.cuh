@@ -14,9 +14,22 @@
 namespace dptb {
 
 // ----------------------------------------------------------------------------- status word
-// One status block per loaded library per device.  [0] = first error code (0 = ok),
-// [1] = detail (block index), [2] = number of waits that ran out, [3] reserved.
-extern __device__ int g_status[4];
+// One status block per translation unit per device (whole-program device linking is not used, so that the
+// compiler may allocate registers per warp-specialised branch).  [0] = first error code (0 = ok),
+// [1] = detail (block index), [2] = number of waits that ran out, [3] reserved.  Every translation unit registers an
+// accessor with the host-side registry; dptb_status_read() folds the blocks into one.
+static __device__ int g_status[4] = {0, 0, 0, 0};
+
+// Host: read (clear == 0) or zero (clear != 0) this translation unit's block.
+static int tu_status_access(int* out4, int clear) {
+  if (clear) {
+    int z[4] = {0, 0, 0, 0};
+    return (int)cudaMemcpyToSymbol(g_status, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out4, g_status, sizeof(int) * 4);
+}
+void register_status_block(int (*access)(int*, int));   // defined once, in gemm.cu
+static const int tu_status_registered = (register_status_block(&tu_status_access), 0);
 
 enum StatusCode : int {
   kOk = 0,
@@ -51,6 +64,17 @@ __device__ __forceinline__ bool elect_one() {
       "selp.b32 %0, 1, 0, P;\n\t}\n"
       : "=r"(pred));
   return pred != 0;
+}
+
+// Move registers between the warpgroups of a CTA: every warp of a warpgroup (4 consecutive warps) executes the same
+// one.  `inc` waits until other warpgroups have released enough with `dec`.
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
 
 // ----------------------------------------------------------------------------- mbarrier
@@ -128,6 +152,29 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, ui
       "r"(w)
       : "memory");
 }
+// Tile store shared -> global.  Elements outside the tensor's extents are dropped; x * element size must be a multiple
+// of 16 bytes and no coordinate may be negative.  Completion is tracked per thread in bulk groups.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until the bulk stores committed by this thread have finished READING shared memory (the source is reusable).
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Wait until the bulk stores committed by this thread have completed.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// 16-byte load that does not allocate in L1 (streamed epilogue inputs; the location may be overwritten later by the
+// same kernel, so this is not a read-only-cache load).
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
 // Generic-proxy writes to shared memory (st.shared) must be fenced before the async proxy
 // (tcgen05.mma, TMA store) reads them.
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -246,6 +293,19 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// registers -> TMEM, 32 lanes x 32 columns of 32 bit (the mirror image of tmem_ld_32x32).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+      "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+      "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 

@@ -22,7 +22,31 @@
 
 namespace dptb {
 
-__device__ int g_status[4] = {0, 0, 0, 0};
+// Opt-in role timers (compile with -DDPTB_GEMM_PROFILE): per CTA, SM clock cycles each warp role spent waiting.
+//   [0] producer waiting for a free stage   [1] producer total
+//   [2] issuer waiting for a loaded stage   [3] issuer waiting for a free accumulator   [4] issuer total
+//   [5] epilogue warp 0 waiting for a finished accumulator   [6] epilogue warp 0 total   [7] work units
+//   [8] epilogue warp 0: accumulator loads (TMEM -> registers)   [9] epilogue warp 0: math + stores   [10] blocks
+#ifdef DPTB_GEMM_PROFILE
+constexpr int kProfSlots = 12;
+__device__ unsigned long long g_gemm_prof[256][kProfSlots];
+#define DPTB_PROF_DECL(name) long long name = 0
+#define DPTB_PROF_BEGIN(t) const long long t = clock64()
+#define DPTB_PROF_END(t, acc) acc += clock64() - t
+#define DPTB_PROF_STORE(slot, v) g_gemm_prof[blockIdx.x & 255][slot] += (unsigned long long)(v)
+#else
+#define DPTB_PROF_DECL(name)
+#define DPTB_PROF_BEGIN(t)
+#define DPTB_PROF_END(t, acc)
+#define DPTB_PROF_STORE(slot, v)
+#endif
+
+// Registry of the per-translation-unit status blocks (filled by static initialisers at load time).
+static int (*g_status_blocks[64])(int*, int);
+static int g_num_status_blocks = 0;
+void register_status_block(int (*access)(int*, int)) {
+  if (g_num_status_blocks < 64) g_status_blocks[g_num_status_blocks++] = access;
+}
 
 // Tensor-parallel all-reduce epilogue (row-parallel Linear: every rank holds a K-slice of the weight and produces a
 // partial [M, N]; the sum over ranks, plus bias / residual, must reach every rank).  world == 0 switches it off.
@@ -67,6 +91,7 @@ struct GemmParams {
   int accumulate;  // C += result
   float alpha;
   int vec_ok;      // all pointers 16-byte aligned and leading dimensions multiples of 8 elements
+  int row_epi;     // row-per-thread register epilogue for bf16 C: 0 off (staged), 1 = 16-byte, 2 = 32-byte accesses
   int tiles_m, tiles_n, num_kb;
   // Split-K: each tile's K range is cut into `splits` work units of kb_per_split k-blocks; partial accumulators go
   // through `ws` (fp32, [tile][split][BN][128]) and the last unit of a tile to finish (per-tile counter) folds them in
@@ -410,6 +435,141 @@ __device__ __forceinline__ void epilogue_direct_f32(const GemmParams& p, long lo
   }
 }
 
+// ----------------------------------------------------------------------------- row-per-thread epilogue
+// One 32-row x 64-column block of a bf16 output.  Each thread owns one row (the TMEM mapping) and keeps its 64 values
+// in registers through the whole epilogue: no shared-memory round trip, no warp synchronisation, and every stage
+// (scale, bias, activation, residual, ...) is one fully unrolled pass over the 64 values behind a warp-uniform branch,
+// so the loads, conversions and stores of a stage are independent and overlap.  A thread reads and writes its row in
+// 32-byte pieces (whole sectors) when the buffers allow it, else in 16-byte pieces.  Measured with the role timers of
+// this file, the staged variant (registers -> shared memory -> lanes re-mapped to whole 128-byte lines) spends about
+// 3700 cycles per block on dependent shared-memory round trips; a variant that handed the staged block to a TMA tile
+// store was slower still (it waits for the copy engine to drain the staging block).
+struct EpiIn {
+  uint4 v[8];
+  int kind;   // 0 none, 1 aux_in, 2 residual, 3 C (accumulate)
+};
+__device__ __forceinline__ void ld_row64(const __nv_bfloat16* s, bool wide, uint4 (&v)[8]) {
+  if (wide) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      asm volatile("ld.global.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=r"(v[2 * g].x), "=r"(v[2 * g].y), "=r"(v[2 * g].z), "=r"(v[2 * g].w), "=r"(v[2 * g + 1].x),
+                     "=r"(v[2 * g + 1].y), "=r"(v[2 * g + 1].z), "=r"(v[2 * g + 1].w)
+                   : "l"(s + g * 16));
+  } else {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) v[g] = ld_stream_v4(s + g * 8);
+  }
+}
+__device__ __forceinline__ void st_row64(__nv_bfloat16* d, bool wide, const uint4 (&v)[8]) {
+  if (wide) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                   ::"l"(d + g * 16), "r"(v[2 * g].x), "r"(v[2 * g].y), "r"(v[2 * g].z), "r"(v[2 * g].w),
+                   "r"(v[2 * g + 1].x), "r"(v[2 * g + 1].y), "r"(v[2 * g + 1].z), "r"(v[2 * g + 1].w)
+                   : "memory");
+  } else {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(d + g * 8) = v[g];
+  }
+}
+__device__ __forceinline__ void add_row64(float (&v)[64], const uint4 (&t)[8]) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float f[8];
+    unpack8(t[g], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[g * 8 + e] += f[e];
+  }
+}
+// Requests the first per-element input of the block (and the bias slice) before the accumulator load is waited for.
+__device__ __forceinline__ void epi_prefetch(const GemmParams& p, uint32_t* bias_s, long long row, long long col0,
+                                             int lane, EpiIn& in) {
+  const __nv_bfloat16* src = nullptr;
+  long long ld = 0;
+  in.kind = 0;
+  if (p.act >= 11) { src = p.aux_in; ld = p.ld_aux_in; in.kind = 1; }
+  else if (p.residual) { src = p.residual; ld = p.ldr; in.kind = 2; }
+  else if (p.accumulate) { src = static_cast<const __nv_bfloat16*>(p.C); ld = p.ldc; in.kind = 3; }
+  if (in.kind != 0 && row < p.M) {
+    ld_row64(src + row * ld + col0, p.row_epi == 2, in.v);
+  } else {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) in.v[g] = make_uint4(0, 0, 0, 0);
+  }
+  if (p.bias) bias_s[lane] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col0) + lane);
+}
+__device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32_t* bias_s, long long row0,
+                                               long long col0, int lane, const uint32_t (&r0)[32],
+                                               const uint32_t (&r1)[32], const EpiIn& in) {
+  const long long row = row0 + lane;
+  const bool live = row < p.M;
+  const bool wide = p.row_epi == 2;
+  float v[64];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = __uint_as_float(r0[i]);
+    v[32 + i] = __uint_as_float(r1[i]);
+  }
+  if (p.alpha != 1.0f) {
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] *= p.alpha;
+  }
+  if (p.bias) {
+    __syncwarp();   // the bias slice written by epi_prefetch is visible
+    uint4 b[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) b[g] = *reinterpret_cast<const uint4*>(bias_s + g * 4);
+    add_row64(v, b);
+    __syncwarp();   // all lanes have read it before the next block overwrites it
+  }
+  if (p.aux_out) {
+    uint4 o[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
+    if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
+  }
+  if (p.act >= 1 && p.act <= 4) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) apply_act8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]));
+  }
+  if (p.act >= 11) {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float x[8];
+      unpack8(in.v[g], x);
+      apply_act_bwd8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]), x);
+    }
+  }
+  if (p.residual) {
+    if (in.kind == 2) {
+      add_row64(v, in.v);
+    } else {
+      uint4 t[8];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) t[g] = make_uint4(0, 0, 0, 0);
+      if (live) ld_row64(p.residual + row * p.ldr + col0, wide, t);
+      add_row64(v, t);
+    }
+  }
+  if (p.accumulate) {
+    if (in.kind == 3) {
+      add_row64(v, in.v);
+    } else {
+      uint4 t[8];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) t[g] = make_uint4(0, 0, 0, 0);
+      if (live) ld_row64(static_cast<const __nv_bfloat16*>(p.C) + row * p.ldc + col0, wide, t);
+      add_row64(v, t);
+    }
+  }
+  uint4 o[8];
+#pragma unroll
+  for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
+  if (live) st_row64(static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0, wide, o);
+}
+
 // ----------------------------------------------------------------------------- all-reduce epilogue helpers
 // Copy the staged 32 x 64 bf16 block (swizzled) into this rank's partial buffer (rows of 128 bytes, contiguous).
 __device__ __forceinline__ void ar_store_partial(const GemmParams& p, const uint8_t* stage, __nv_bfloat16* blk,
@@ -484,8 +644,10 @@ struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageOff = STAGES * (kABytes + kBBytes);   // epilogue staging: 4 KB per epilogue warp
-  static constexpr int kBarOffset = kStageOff + kEpiWarps * 4096;
+  static constexpr int kBiasOff = kStageOff + kEpiWarps * 4096;    // 64 bf16 bias values per epilogue warp
+  static constexpr int kBarOffset = kBiasOff + kEpiWarps * 128;
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1) * 8 + 32 + 1024;  // + alignment slack
+  static_assert(kTotal <= 227 * 1024, "GEMM: shared memory budget");
 };
 
 template <bool A_MN, bool B_MN, int BN, int STAGES>
@@ -546,6 +708,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t issued = 0;
+      DPTB_PROF_DECL(prof_wait);
+      DPTB_PROF_BEGIN(prof_t_all);
       for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x) {
         const int tile = unit % num_tiles;
         const int kb0 = (unit / num_tiles) * p.kb_per_split;
@@ -555,7 +719,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; ++kb, ++issued) {
           const int s = issued % STAGES;
           const uint32_t ph = (issued / STAGES) & 1;
+          DPTB_PROF_BEGIN(prof_t0);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) break;
+          DPTB_PROF_END(prof_t0, prof_wait);
           mbar_arrive_expect_tx(&full_bar[s], L::kABytes + L::kBBytes);
           uint8_t* a_dst = sA + s * L::kABytes;
           uint8_t* b_dst = sB + s * L::kBBytes;
@@ -573,6 +739,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
+      DPTB_PROF_STORE(0, prof_wait);
+      DPTB_PROF_STORE(1, clock64() - prof_t_all);
       if (*abort_flag) {
         // Do not leave while a tile copy may still be writing this CTA's shared memory.
         const uint32_t n = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
@@ -595,19 +763,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t consumed = 0;
       uint32_t local_tile = 0;
       bool issued_any = false;
+      DPTB_PROF_DECL(prof_wait_full);
+      DPTB_PROF_DECL(prof_wait_acc);
+      DPTB_PROF_BEGIN(prof_t_all);
       for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
         const int kb0 = (unit / num_tiles) * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
+        DPTB_PROF_BEGIN(prof_t1);
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, kWaitTmemEmptyTimeout)) break;
+        DPTB_PROF_END(prof_t1, prof_wait_acc);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb, ++consumed) {
           const int s = consumed % STAGES;
           const uint32_t ph = (consumed / STAGES) & 1;
+          DPTB_PROF_BEGIN(prof_t0);
           if (!mbar_wait(&full_bar[s], ph, abort_flag, kWaitFullTimeout)) { ok = false; break; }
+          DPTB_PROF_END(prof_t0, prof_wait_full);
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(sA + s * L::kABytes);
           const uint32_t b_addr = smem_u32(sB + s * L::kBBytes);
@@ -623,6 +798,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!ok) break;
         umma_commit(&tmem_full[acc]);  // accumulator complete
       }
+      DPTB_PROF_STORE(2, prof_wait_full);
+      DPTB_PROF_STORE(3, prof_wait_acc);
+      DPTB_PROF_STORE(4, clock64() - prof_t_all);
+      DPTB_PROF_STORE(7, local_tile);
       if (*abort_flag && issued_any) {
         umma_commit(drain_bar);
         uint64_t t0 = global_timer_ns();
@@ -666,6 +845,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         __syncwarp();
       }
     };
+    uint32_t* bias_s = reinterpret_cast<uint32_t*>(smem + L::kBiasOff) + ew * 32;
     // Bounded barrier over the epilogue warps (a hardware named barrier could not give up).
     auto epi_sync = [&]() -> bool {
       __syncwarp();
@@ -692,6 +872,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       return !*abort_flag;
     };
+    DPTB_PROF_DECL(prof_wait_acc);
+    DPTB_PROF_DECL(prof_ld);
+    DPTB_PROF_DECL(prof_fin);
+    DPTB_PROF_DECL(prof_blocks);
+    DPTB_PROF_BEGIN(prof_t_all);
     for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
       const int tile = unit % num_tiles;
       const int split = unit / num_tiles;
@@ -699,7 +884,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int n0 = (tile / p.tiles_m) * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
+      DPTB_PROF_BEGIN(prof_t0);
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout))) break;
+      DPTB_PROF_END(prof_t0, prof_wait_acc);
       tc_fence_after_sync();
       const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
@@ -758,10 +945,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const long long col0 = (long long)n0 + c * 64;
           if (col0 >= p.N) break;  // warp-uniform
           uint32_t r0[32], r1[32];
+          DPTB_PROF_BEGIN(prof_c0);
           tmem_ld_32x32(t_row + c * 64, r0);
           tmem_ld_32x32(t_row + c * 64 + 32, r1);
-          tmem_ld_wait();
-          emit(row0, col0, r0, r1);
+          if (p.row_epi && col0 + 64 <= p.N) {
+            EpiIn in;
+            epi_prefetch(p, bias_s, row0 + lane, col0, lane, in);
+            tmem_ld_wait();
+            DPTB_PROF_END(prof_c0, prof_ld);
+            DPTB_PROF_BEGIN(prof_c1);
+            epi_finish_row(p, bias_s, row0, col0, lane, r0, r1, in);
+            DPTB_PROF_END(prof_c1, prof_fin);
+          } else {
+            tmem_ld_wait();
+            DPTB_PROF_END(prof_c0, prof_ld);
+            DPTB_PROF_BEGIN(prof_c1);
+            emit(row0, col0, r0, r1);
+            DPTB_PROF_END(prof_c1, prof_fin);
+          }
+#ifdef DPTB_GEMM_PROFILE
+          ++prof_blocks;
+#endif
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -804,6 +1008,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const long long col0 = (long long)n0 + c * 64;
             if (col0 >= p.N) break;
             uint32_t r0[32], r1[32];
+            const bool tma = p.row_epi && col0 + 64 <= p.N;
+            EpiIn in;
+            if (tma) epi_prefetch(p, bias_s, row0 + lane, col0, lane, in);
             // Split index outermost: the 32 loads of one split are independent and stay in flight together; the
             // additions still happen in split order for every element.
 #pragma unroll
@@ -822,12 +1029,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 else r1[i] = __float_as_uint(acc32[i]);
               }
             }
-            emit(row0, col0, r0, r1);
+            if (tma) epi_finish_row(p, bias_s, row0, col0, lane, r0, r1, in);
+            else emit(row0, col0, r0, r1);
           }
         }
         if (!epi_sync()) break;  // epi_last may be rewritten only after every warp has read it
       }
     }
+#ifdef DPTB_GEMM_PROFILE
+    if (ew == 0 && lane == 0) {
+      DPTB_PROF_STORE(5, prof_wait_acc);
+      DPTB_PROF_STORE(6, clock64() - prof_t_all);
+      DPTB_PROF_STORE(8, prof_ld);
+      DPTB_PROF_STORE(9, prof_fin);
+      DPTB_PROF_STORE(10, prof_blocks);
+    }
+#endif
   }
 
   tc_fence_before_sync();
@@ -1071,6 +1288,20 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream
   else            rc = encode_tmap_2d_bf16(&tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb * 2, 64, 64);
   if (rc) return rc;
 
+  // bf16 outputs take the row-per-thread register epilogue (DPTB_GEMM_STAGED_EPILOGUE=1 keeps the staged one, for
+  // comparisons); 32-byte accesses when every per-element buffer allows them.
+  static const bool staged_only = [] {
+    const char* e = getenv("DPTB_GEMM_STAGED_EPILOGUE");
+    return e && e[0] == '1';
+  }();
+  p.row_epi = (!ar && !staged_only && !p.out_f32 && p.vec_ok && !(p.bias && p.bias_f32)) ? 1 : 0;
+  if (p.row_epi) {
+    auto wide_ok = [](const void* q, long long ld) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0 && ld % 16 == 0; };
+    if (wide_ok(p.C, p.ldc) && (!p.residual || wide_ok(p.residual, p.ldr)) &&
+        (!p.aux_out || wide_ok(p.aux_out, p.ld_aux_out)) && (!p.aux_in || wide_ok(p.aux_in, p.ld_aux_in)))
+      p.row_epi = 2;
+  }
+
   const bool amn = a->trans_a != 0, bmn = a->trans_b == 0;
 #define DPTB_LAUNCH(AMN, BMN)                                                        \
   (bn == 256 ? launch_tc<AMN, BMN, 256, 4>(tmA, tmB, p, stream) : launch_tc<AMN, BMN, 128, 6>(tmA, tmB, p, stream))
@@ -1091,12 +1322,38 @@ extern "C" int dptb_gemm_allreduce(const DptbGemmArgs* a, const DptbTpArArgs* ar
 }
 
 // Status word access ------------------------------------------------------------------------------
+// Folds the blocks of all translation units: the first non-zero code (with its detail) and the total number of
+// waits that ran out.
 extern "C" int dptb_status_read(int* out4) {
-  return (int)cudaMemcpyFromSymbol(out4, g_status, sizeof(int) * 4);
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+  for (int i = 0; i < g_num_status_blocks; ++i) {
+    int b[4] = {0, 0, 0, 0};
+    const int rc = g_status_blocks[i](b, 0);
+    if (rc) return rc;
+    if (out4[0] == 0 && b[0] != 0) { out4[0] = b[0]; out4[1] = b[1]; }
+    out4[2] += b[2];
+  }
+  return 0;
 }
 extern "C" int dptb_status_clear() {
-  int z[4] = {0, 0, 0, 0};
-  return (int)cudaMemcpyToSymbol(g_status, z, sizeof(z));
+  for (int i = 0; i < g_num_status_blocks; ++i) {
+    const int rc = g_status_blocks[i](nullptr, 1);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// Role timers (see DPTB_GEMM_PROFILE): copies [256][12] counters out and zeroes them; -5 when not compiled in.
+extern "C" int dptb_gemm_profile_read(unsigned long long* out) {
+#ifdef DPTB_GEMM_PROFILE
+  int rc = (int)cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(unsigned long long) * 256 * kProfSlots);
+  if (rc) return rc;
+  static unsigned long long zeros[256 * kProfSlots];
+  return (int)cudaMemcpyToSymbol(g_gemm_prof, zeros, sizeof(zeros));
+#else
+  (void)out;
+  return kErrUnsupported;
+#endif
 }
 
 extern "C" long long dptb_launch_count() { return launch_counter(); }

@@ -58,6 +58,42 @@ def test_gemm_epilogue_forward(act):
     assert _rel_err(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize("act", [None, "gelu_tanh", "silu"])
+@pytest.mark.parametrize("M,N,Kd,bn", [(512, 384, 256, 128), (1000, 760, 264, 256), (300, 2304, 768, 256)])
+def test_gemm_epilogue_forward_bf16_bias(act, M, N, Kd, bn):
+    """bf16 bias: the row-per-thread epilogue with TMA tile stores (ragged M is clipped by the store, the ragged last
+    column block takes the staged path)."""
+    a, w = _mk((M, Kd), seed=3), _mk((N, Kd), scale=0.05, seed=4)
+    bias = _mk((N,), seed=5)
+    res = _mk((M, N), seed=6)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    pre = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.gemm(a, w, out, trans_b=True, bias=bias, residual=res, aux_out=pre, act=act, bn=bn)
+    pre_ref = a.float() @ w.float().t() + bias.float()
+    ref = R.ACTIVATIONS[act](pre_ref) + res.float()
+    assert torch.isfinite(out.float()).all() and torch.isfinite(pre.float()).all()
+    assert _rel_err(pre, pre_ref) < 1e-2
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_gemm_epilogue_in_place_residual_accumulate_and_padding():
+    M, N, Kd = 640, 200, 192
+    a, w = _mk((M, Kd), seed=21), _mk((N, Kd), scale=0.05, seed=22)
+    # residual aliases the output (x += a @ w^T), output rows padded to 256 columns that must stay untouched
+    buf = torch.zeros(M, 256, dtype=torch.bfloat16, device="cuda")
+    base = _mk((M, N), seed=23)
+    buf[:, :N] = base
+    buf[:, N:] = 7.0
+    K.gemm(a, w, buf, trans_b=True, residual=buf, n_cols=N)
+    ref = base.float() + a.float() @ w.float().t()
+    assert _rel_err(buf[:, :N], ref) < 1e-2
+    assert bool((buf[:, N:] == 7.0).all())
+    # accumulate into a bf16 output
+    out = base.clone()
+    K.gemm(a, w, out, trans_b=True, accumulate=True)
+    assert _rel_err(out, ref) < 1e-2
+
+
 @pytest.mark.parametrize("act", ["relu", "gelu_tanh", "quick_gelu", "silu"])
 def test_gemm_epilogue_act_backward(act):
     M, N, Kd = 256, 256, 128
