@@ -10,10 +10,13 @@
 //   S  = Q K^T          dP = dO V^T                       (into TMEM, rows = queries)
 //   dV += P^T dO        dK += dS^T Q                      (accumulate in TMEM across the whole loop, rows = keys)
 //   dQ  = dS K                                            (TMEM -> shared staging -> fp32 reduction into dq_acc)
-// with P = exp2(S*c - lse) and dS = scale * P * (dP - delta) computed by one thread per query row in between and
-// written to shared memory in a layout that serves both as a K-major operand (dS K) and, transposed, as an
-// MN-major operand (P^T dO, dS^T Q).
-//   warps 0-3  compute warpgroup      warp 4  TMA producer      warp 5  MMA issuer
+// with P = exp2(S*c - lse) and dS = scale * P * (dP - delta) computed in between and written to shared memory in a
+// layout that serves both as a K-major operand (dS K) and, transposed, as an MN-major operand (P^T dO, dS^T Q).
+//   warps 0-7  two compute warpgroups: thread = one query row x one half (64 keys) of the S / dP tiles.  A thread pulls
+//              its 64 scores and 64 dP values from TMEM in one go and hands the columns straight back, so the tensor core
+//              computes S / dP of the next query tile while P / dS of this one are formed; it then drains its quarter
+//              of the previous tile's dQ (TMEM -> shared staging -> fp32 reduction into dq_acc)
+//   warp 8     TMA producer      warp 9     MMA issuer      (warps 10-11 only take part in the register hand-over)
 #include <cuda_bf16.h>
 
 #include "common/host.h"
@@ -42,9 +45,26 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// Opt-in phase timers (compile with -DDPTB_ATTN_PROFILE), SM clock cycles summed over all CTAs:
+//   compute thread 0:  [0] wait S/dP  [1] TMEM -> registers  [2] P / dS math  [3] wait for the previous products
+//                      [4] stores + signal  [5] dQ drain  [6] loop total  [7] iterations
+//   MMA issuer:        [8] wait Q/dO  [9] wait S/dP drained  [10] wait P/dS  [11] wait dQ drained  [12] loop total
+#ifdef DPTB_ATTN_PROFILE
+__device__ unsigned long long g_attn_bwd_prof[16];
+#define BWD_PROF_MARK(t) const long long t = clock64()
+#define BWD_PROF_ADD(slot, t0, t1) prof_acc[slot] += (t1) - (t0)
+#else
+#define BWD_PROF_MARK(t)
+#define BWD_PROF_ADD(slot, t0, t1)
+#endif
+
 constexpr int kBwdHD = 64;
 constexpr int kBwdTile = 128;
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 384;
+// Registers per thread after the hand-over (the CTA starts with 384 x 168 and the pool does not grow).
+constexpr int kBwdComputeRegs = 216;
+constexpr int kBwdProducerRegs = 72;
+static_assert(2 * 128 * kBwdComputeRegs + 128 * kBwdProducerRegs <= kBwdThreads * 168, "register hand-over must balance");
 constexpr int kBwdStages = 2;
 constexpr int kDqStride = 68;  // floats per staged dQ row (padding keeps 16-byte accesses conflict-free)
 
@@ -60,7 +80,7 @@ struct AttnBwdSmem {
   static constexpr int kDqOff = kDSOff + kPBytes;
   static constexpr int kDqBytes = kBwdTile * kDqStride * 4;
   static constexpr int kBarOff = kDqOff + kDqBytes;
-  static constexpr int kNumBars = 1 + 2 * kBwdStages + 6;
+  static constexpr int kNumBars = 1 + 2 * kBwdStages + 7;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16 + 1024;
 };
 
@@ -78,8 +98,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = kv_full + 1;               // [stages]
   uint64_t* qdo_empty = qdo_full + kBwdStages;    // [stages]
-  uint64_t* sdp_full = qdo_empty + kBwdStages;
-  uint64_t* pds_full = sdp_full + 1;
+  uint64_t* sdp_full = qdo_empty + kBwdStages;    // S and dP of the current query tile are in TMEM
+  uint64_t* sdp_empty = sdp_full + 1;             // ... and have been copied to registers by all 256 compute threads
+  uint64_t* pds_full = sdp_empty + 1;             // P and dS are in shared memory
   uint64_t* dq_full = pds_full + 1;
   uint64_t* dq_empty = dq_full + 1;
   uint64_t* dkv_full = dq_empty + 1;
@@ -108,7 +129,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmDO);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0) {
       mbar_init(kv_full, 1);
       for (int s = 0; s < kBwdStages; ++s) {
@@ -116,9 +137,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mbar_init(&qdo_empty[s], 1);
       }
       mbar_init(sdp_full, 1);
-      mbar_init(pds_full, kBwdTile);
+      mbar_init(sdp_empty, 2 * kBwdTile);
+      mbar_init(pds_full, 2 * kBwdTile);
       mbar_init(dq_full, 1);
-      mbar_init(dq_empty, kBwdTile);
+      mbar_init(dq_empty, 2 * kBwdTile);
       mbar_init(dkv_full, 1);
       mbar_init(drain_bar, 1);
       mbar_fence_init();
@@ -131,7 +153,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp >= 8) {
+    warpgroup_reg_dec<kBwdProducerRegs>();
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && total_iters > 0) {
       mbar_arrive_expect_tx(kv_full, 2 * L::kTileBytes);
@@ -157,7 +181,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                  global_timer_ns() - t0 < kWaitLimitNs / 4) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && total_iters > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kBwdTile, kBwdTile, false, false);   // S, dP
@@ -167,12 +191,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t p_addr = smem_u32(smem + L::kPOff), ds_addr = smem_u32(smem + L::kDSOff);
       bool ok = mbar_wait(kv_full, 0, abort_flag, kWaitFullTimeout);
       bool issued_any = false;
-      for (int it = 0; it < total_iters && ok; ++it) {
+      // S = Q K^T and dP = dO V^T of query tile `it` (operands in stage it % stages).
+      auto issue_sdp = [&](int it) {
         const int s = it % kBwdStages;
-        const uint32_t ph = (it / kBwdStages) & 1;
-        ok = mbar_wait(&qdo_full[s], ph, abort_flag, kWaitFullTimeout);
-        if (!ok) break;
-        tc_fence_after_sync();
         const uint32_t q_addr = smem_u32(smem + L::kQOff + s * L::kTileBytes);
         const uint32_t do_addr = smem_u32(smem + L::kDOOff + s * L::kTileBytes);
 #pragma unroll
@@ -185,7 +206,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     make_smem_desc(v_addr + kk * 32, 16, 1024), idesc_s, kk != 0);
         umma_commit(sdp_full);
         issued_any = true;
+      };
+      if (ok) ok = mbar_wait(&qdo_full[0], 0, abort_flag, kWaitFullTimeout);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_sdp(0);
+      }
+#ifdef DPTB_ATTN_PROFILE
+      long long prof_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+      const long long prof_begin = clock64();
+#endif
+      for (int it = 0; it < total_iters && ok; ++it) {
+        const int s = it % kBwdStages;
+        const uint32_t q_addr = smem_u32(smem + L::kQOff + s * L::kTileBytes);
+        const uint32_t do_addr = smem_u32(smem + L::kDOOff + s * L::kTileBytes);
+        // (a) S / dP of the next query tile, as soon as the compute warps have copied this tile's out of TMEM.
+        if (it + 1 < total_iters) {
+          const int s1 = (it + 1) % kBwdStages;
+          BWD_PROF_MARK(m0);
+          ok = mbar_wait(&qdo_full[s1], ((it + 1) / kBwdStages) & 1, abort_flag, kWaitFullTimeout);
+          BWD_PROF_MARK(m1);
+          if (ok) ok = mbar_wait(sdp_empty, it & 1, abort_flag, kWaitTmemEmptyTimeout);
+          BWD_PROF_MARK(m2);
+          BWD_PROF_ADD(8, m0, m1);
+          BWD_PROF_ADD(9, m1, m2);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_sdp(it + 1);
+        }
+        // (b) the three products that consume P / dS of this tile.
+        BWD_PROF_MARK(m3);
         ok = mbar_wait(pds_full, it & 1, abort_flag, kWaitFlagTimeout);
+        BWD_PROF_MARK(m4);
+        BWD_PROF_ADD(10, m3, m4);
         if (!ok) break;
         tc_fence_after_sync();
         // dV += P^T dO ; dK += dS^T Q    (A: [q rows][keys] read as MN-major, B: [q rows][hd] read as MN-major)
@@ -198,7 +251,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           umma_bf16(tmem_base + kDKCol, make_smem_desc(ds_addr + kk * 2048, kBwdTile * 128, 1024),
                     make_smem_desc(q_addr + kk * 2048, kBwdTile * 128, 1024), idesc_kv, (it | kk) != 0);
         if (it > 0) {
+          BWD_PROF_MARK(m5);
           ok = mbar_wait(dq_empty, (it - 1) & 1, abort_flag, kWaitFlagTimeout);
+          BWD_PROF_MARK(m6);
+          BWD_PROF_ADD(11, m5, m6);
           if (!ok) break;
           tc_fence_after_sync();
         }
@@ -210,7 +266,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                     make_smem_desc(k_addr + kk * 2048, kBwdTile * 128, 1024), idesc_q, kk != 0);
         umma_commit(dq_full);
         umma_commit(&qdo_empty[s]);
+        issued_any = true;
       }
+#ifdef DPTB_ATTN_PROFILE
+      prof_acc[12] = clock64() - prof_begin;
+      for (int i = 8; i < 13; ++i) atomicAdd(&g_attn_bwd_prof[i], (unsigned long long)prof_acc[i]);
+#endif
       if (ok) umma_commit(dkv_full);
       if (*abort_flag && issued_any) {
         umma_commit(drain_bar);
@@ -218,39 +279,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         while (!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < kWaitLimitNs / 4) {}
       }
     }
+  }
   } else {
-    // ------------------------------------------------------------------ compute warpgroup
-    const int q = warp & 3;
+    // ------------------------------------------------------------------ compute warpgroups
+    warpgroup_reg_inc<kBwdComputeRegs>();
+    const int q = warp & 3;          // TMEM lane quarter
+    const int half = warp >> 2;      // which 64 keys of the tile (and which 32 columns of dQ) this thread handles
     const int row = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint8_t* p_tile = smem + L::kPOff;
-    uint8_t* ds_tile = smem + L::kDSOff;
+    uint8_t* p_tile = smem + L::kPOff + half * (kBwdTile * 128);     // 64-key block `half` of the K-major tiles
+    uint8_t* ds_tile = smem + L::kDSOff + half * (kBwdTile * 128);
     float* dq_stage = reinterpret_cast<float*>(smem + L::kDqOff);
     bool ok = true;
 
-    // Drains dQ of iteration `itp` (head hp, query tile ip): TMEM -> staging -> coalesced fp32 reduction.
-    auto flush_dq = [&](int itp, int hp, int ip) -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait(dq_full, itp & 1, abort_flag, kWaitTmemFullTimeout))) return false;
+    // Drains this thread's part of dQ of iteration `itp` (head hp, query tile ip): TMEM -> staging -> fp32 reduction.
+    // Its phase of dq_full has been waited for by the caller.
+    auto flush_dq = [&](int hp, int ip) {
       tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(lane_addr + kDQCol + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          *reinterpret_cast<float4*>(dq_stage + row * kDqStride + c * 32 + i) =
-              make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                          __uint_as_float(r[i + 3]));
-      }
+      uint32_t r[32];
+      tmem_ld_32x32(lane_addr + kDQCol + half * 32, r);
+      tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(dq_empty);
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(dq_stage + row * kDqStride + half * 32 + i) =
+            make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                        __uint_as_float(r[i + 3]));
       __syncwarp();
-      // This warp staged rows [q*32, q*32+32); it also reduces exactly those rows: 2 rows per instruction.
-#pragma unroll 4
-      for (int rr = 0; rr < 32; rr += 2) {
-        const int r_loc = q * 32 + rr + (lane >> 4);
-        const int col = (lane & 15) * 4;
+      // This warp staged rows [q*32, q*32+32) x columns [half*32, half*32+32) and reduces exactly that block:
+      // 4 rows of 128 bytes per instruction.
+#pragma unroll
+      for (int rr = 0; rr < 32; rr += 4) {
+        const int r_loc = q * 32 + rr + (lane >> 3);
+        const int col = half * 32 + (lane & 7) * 4;
         const int qi = ip * kBwdTile + r_loc;
         if (qi < p.Sq) {
           const float4 v = *reinterpret_cast<const float4*>(dq_stage + r_loc * kDqStride + col);
@@ -259,11 +321,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       __syncwarp();
-      return true;
     };
 
     int it = 0;
     int prev_h = 0, prev_i = 0;
+#ifdef DPTB_ATTN_PROFILE
+    long long prof_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_begin = clock64();
+#endif
     for (int g = 0; g < group && ok; ++g) {
       const int head = kv_head * group + g;
       for (int i = i_start; i < n_q_tiles && ok; ++i, ++it) {
@@ -273,53 +338,79 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const float lse_nat = row_ok ? p.lse[stat] : 0.0f;
         const float delta = row_ok ? p.delta[stat] : 0.0f;
         const bool dead = !row_ok || lse_nat == -INFINITY;
-        const float lse2 = lse_nat * 1.4426950408889634f;
+        const float lse2 = dead ? INFINITY : lse_nat * 1.4426950408889634f;   // dead rows: exp2(-inf) = 0
         const int key_limit = p.causal ? min(p.Sk - 1, qi + p.q_offset) : p.Sk - 1;
+        const int kbase = key0 + half * 64;
+        BWD_PROF_MARK(c0);
         ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, abort_flag, kWaitTmemFullTimeout));
         if (!ok) break;
+        BWD_PROF_MARK(c1);
         tc_fence_after_sync();
+        uint32_t rs[64], rp[64];
+        tmem_ld_32x32(lane_addr + kSCol + half * 64, reinterpret_cast<uint32_t(&)[32]>(rs[0]));
+        tmem_ld_32x32(lane_addr + kSCol + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(rs[32]));
+        tmem_ld_32x32(lane_addr + kDPCol + half * 64, reinterpret_cast<uint32_t(&)[32]>(rp[0]));
+        tmem_ld_32x32(lane_addr + kDPCol + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(rp[32]));
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(sdp_empty);   // the tensor core may overwrite S / dP with the next query tile's
+        BWD_PROF_MARK(c2);
+        uint32_t pk_p[32], pk_ds[32];
+        const bool need_mask = kbase + 63 > key_limit;
+#pragma unroll
+        for (int e = 0; e < 64; e += 2) {
+          float p0 = fast_exp2_b(fmaf(__uint_as_float(rs[e]), p.scale_log2, -lse2));
+          float p1 = fast_exp2_b(fmaf(__uint_as_float(rs[e + 1]), p.scale_log2, -lse2));
+          if (need_mask) {
+            if (kbase + e > key_limit) p0 = 0.0f;
+            if (kbase + e + 1 > key_limit) p1 = 0.0f;
+          }
+          const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * p.scale;
+          const float d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * p.scale;
+          pk_p[e >> 1] = pack_bf16x2(p0, p1);
+          pk_ds[e >> 1] = pack_bf16x2(d0, d1);
+        }
+        BWD_PROF_MARK(c3);
         // P / dS of the previous iteration must have been consumed before they are overwritten: every MMA of that
         // iteration has completed once its dq_full phase has.
         if (it > 0) {
           ok = __all_sync(0xffffffffu, mbar_wait(dq_full, (it - 1) & 1, abort_flag, kWaitTmemFullTimeout));
           if (!ok) break;
         }
-#pragma unroll 1
-        for (int c = 0; c < kBwdTile / 32; ++c) {
-          uint32_t rs[32], rp[32];
-          tmem_ld_32x32(lane_addr + kSCol + c * 32, rs);
-          tmem_ld_32x32(lane_addr + kDPCol + c * 32, rp);
-          tmem_ld_wait();
-          uint32_t pk_p[16], pk_ds[16];
+        BWD_PROF_MARK(c4);
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float p0 = fast_exp2_b(__uint_as_float(rs[e]) * p.scale_log2 - lse2);
-            float p1 = fast_exp2_b(__uint_as_float(rs[e + 1]) * p.scale_log2 - lse2);
-            if (dead || key0 + c * 32 + e > key_limit) p0 = 0.0f;
-            if (dead || key0 + c * 32 + e + 1 > key_limit) p1 = 0.0f;
-            const float d0 = p0 * (__uint_as_float(rp[e]) - delta) * p.scale;
-            const float d1 = p1 * (__uint_as_float(rp[e + 1]) - delta) * p.scale;
-            pk_p[e >> 1] = pack_bf16x2(p0, p1);
-            pk_ds[e >> 1] = pack_bf16x2(d0, d1);
-          }
-          const int blk = (c >> 1) * (kBwdTile * 128);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const uint32_t chunk = (uint32_t)((c & 1) * 4 + e) ^ (uint32_t)(row & 7);
-            const int off = blk + row * 128 + chunk * 16;
-            *reinterpret_cast<uint4*>(p_tile + off) = make_uint4(pk_p[e * 4], pk_p[e * 4 + 1], pk_p[e * 4 + 2], pk_p[e * 4 + 3]);
-            *reinterpret_cast<uint4*>(ds_tile + off) = make_uint4(pk_ds[e * 4], pk_ds[e * 4 + 1], pk_ds[e * 4 + 2], pk_ds[e * 4 + 3]);
-          }
+        for (int e = 0; e < 8; ++e) {
+          const int off = row * 128 + (int)(((uint32_t)e ^ (uint32_t)(row & 7)) << 4);
+          *reinterpret_cast<uint4*>(p_tile + off) = make_uint4(pk_p[e * 4], pk_p[e * 4 + 1], pk_p[e * 4 + 2], pk_p[e * 4 + 3]);
+          *reinterpret_cast<uint4*>(ds_tile + off) = make_uint4(pk_ds[e * 4], pk_ds[e * 4 + 1], pk_ds[e * 4 + 2], pk_ds[e * 4 + 3]);
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         mbar_arrive(pds_full);
-        if (it > 0) ok = flush_dq(it - 1, prev_h, prev_i);
+        BWD_PROF_MARK(c5);
+        if (it > 0) flush_dq(prev_h, prev_i);
+        BWD_PROF_MARK(c6);
+        BWD_PROF_ADD(0, c0, c1);
+        BWD_PROF_ADD(1, c1, c2);
+        BWD_PROF_ADD(2, c2, c3);
+        BWD_PROF_ADD(3, c3, c4);
+        BWD_PROF_ADD(4, c4, c5);
+        BWD_PROF_ADD(5, c5, c6);
         prev_h = head;
         prev_i = i;
       }
     }
-    if (ok && total_iters > 0) ok = flush_dq(total_iters - 1, prev_h, prev_i);
+#ifdef DPTB_ATTN_PROFILE
+    if (threadIdx.x == 0) {
+      prof_acc[6] = clock64() - prof_begin;
+      prof_acc[7] = it;
+      for (int i = 0; i < 8; ++i) atomicAdd(&g_attn_bwd_prof[i], (unsigned long long)prof_acc[i]);
+    }
+#endif
+    if (ok && total_iters > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(dq_full, (total_iters - 1) & 1, abort_flag, kWaitTmemFullTimeout));
+      if (ok) flush_dq(prev_h, prev_i);
+    }
 
     // dK / dV of this key tile.
     const int key = key0 + row;
@@ -327,7 +418,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (key < p.Sk) {
         __nv_bfloat16* dkp = p.dk + ((long long)batch * p.Sk + key) * p.lddk + (long long)kv_head * HD;
         __nv_bfloat16* dvp = p.dv + ((long long)batch * p.Sk + key) * p.lddv + (long long)kv_head * HD;
-        for (int d = 0; d < HD; d += 8) {
+        for (int d = half * 32; d < half * 32 + 32; d += 8) {
           *reinterpret_cast<uint4*>(dkp + d) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(dvp + d) = make_uint4(0, 0, 0, 0);
         }
@@ -339,8 +430,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __nv_bfloat16* base = which == 0 ? p.dv : p.dk;
         const long long ld = which == 0 ? p.lddv : p.lddk;
         const uint32_t col0 = which == 0 ? kDVCol : kDKCol;
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        {
+          const int c = half;   // each compute warpgroup writes 32 of the 64 columns
           uint32_t r[32];
           tmem_ld_32x32(lane_addr + col0 + c * 32, r);
           tmem_ld_wait();
@@ -364,7 +455,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc<TMEM_COLS>(tmem_base);
   }
@@ -441,6 +532,19 @@ struct DptbAttnBwdArgs {
   int causal, q_offset;
   float scale;
 };
+
+// Phase timers (see DPTB_ATTN_PROFILE): copies the 16 counters out and zeroes them; -5 when not compiled in.
+extern "C" int dptb_attn_bwd_profile_read(unsigned long long* out) {
+#ifdef DPTB_ATTN_PROFILE
+  int rc = (int)cudaMemcpyFromSymbol(out, g_attn_bwd_prof, sizeof(unsigned long long) * 16);
+  if (rc) return rc;
+  static unsigned long long zeros[16];
+  return (int)cudaMemcpyToSymbol(g_attn_bwd_prof, zeros, sizeof(zeros));
+#else
+  (void)out;
+  return kErrUnsupported;
+#endif
+}
 
 extern "C" int dptb_attn_bwd(const DptbAttnBwdArgs* a, void* stream) {
   auto st = static_cast<cudaStream_t>(stream);

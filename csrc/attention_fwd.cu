@@ -53,6 +53,18 @@ constexpr int kProducerRegs = 72;
 static_assert(2 * 128 * kSoftmaxRegs + 128 * kProducerRegs <= kAttnThreads * 168, "register hand-over must balance");
 constexpr float kLazyMaxSlack = 8.0f;   // log2 units a row's maximum may grow before O is rescaled
 
+// Opt-in phase timers (compile with -DDPTB_ATTN_PROFILE): SM clock cycles that thread 0 of softmax warpgroup 0 spent,
+// summed per CTA:  [0] waiting for S   [1] S: TMEM -> registers   [2] mask + maximum   [3] rescale of O
+// [4] waiting for the previous P.V   [5] exp2 + pack + shared-memory stores   [6] whole loop   [7] KV tiles
+#ifdef DPTB_ATTN_PROFILE
+__device__ unsigned long long g_attn_prof[8];
+#define ATTN_PROF_MARK(t) const long long t = clock64()
+#define ATTN_PROF_ADD(slot, t0, t1) prof_acc[slot] += (t1) - (t0)
+#else
+#define ATTN_PROF_MARK(t)
+#define ATTN_PROF_ADD(slot, t0, t1)
+#endif
+
 template <int HD, int NQ, int KST, int VST>
 struct AttnFwdSmem {
   static constexpr int kQBytes = kAttnBM * HD * 2;
@@ -285,10 +297,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float l_run = 0.0f;
     const int key_limit = p.causal ? min(p.Sk - 1, q_row + p.q_offset) : p.Sk - 1;  // last visible key of this row
     bool ok = true;
+#ifdef DPTB_ATTN_PROFILE
+    long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_begin = clock64();
+#endif
 
     for (int j = 0; j < n && ok; ++j) {
+      ATTN_PROF_MARK(pt0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, kWaitTmemFullTimeout));
       if (!ok) break;
+      ATTN_PROF_MARK(pt1);
       tc_fence_after_sync();
       uint32_t s[kAttnBN];
 #pragma unroll
@@ -296,6 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&s_empty[t]);   // the tensor core may overwrite S_t with the next tile's scores
+      ATTN_PROF_MARK(pt2);
 
       const int key0 = j * kAttnBN;
       if (key0 + kAttnBN - 1 > key_limit) {   // per-thread; no warp-level operation inside
@@ -312,6 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
       }
       const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      ATTN_PROF_MARK(pt3);
       // Lazy maximum: move it only when some row of this warp outgrew its old one by more than the slack (the first
       // finite tile always does: -inf + slack = -inf).  Rows that move rescale what they have accumulated so far.
       if (__any_sync(0xffffffffu, m_tile > m_use + kLazyMaxSlack)) {
@@ -336,11 +356,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         m_use = m_new;
       }
       const float m_sub = (m_use == -INFINITY) ? 0.0f : m_use;
+      ATTN_PROF_MARK(pt4);
       // The previous P_t must have been consumed before it is overwritten (it nearly always has been by now).
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (j - 1) & 1, abort_flag, kWaitTmemFullTimeout));
         if (!ok) break;
       }
+      ATTN_PROF_MARK(pt5);
       // Probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle), row sum.
       float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll
@@ -369,7 +391,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(&p_full[t]);
+      ATTN_PROF_MARK(pt6);
+      ATTN_PROF_ADD(0, pt0, pt1);
+      ATTN_PROF_ADD(1, pt1, pt2);
+      ATTN_PROF_ADD(2, pt2, pt3);
+      ATTN_PROF_ADD(3, pt3, pt4);
+      ATTN_PROF_ADD(4, pt4, pt5);
+      ATTN_PROF_ADD(5, pt5, pt6);
     }
+#ifdef DPTB_ATTN_PROFILE
+    if (threadIdx.x == 0) {
+      prof_acc[6] = clock64() - prof_begin;
+      prof_acc[7] = n;
+      for (int i = 0; i < 8; ++i) atomicAdd(&g_attn_prof[i], (unsigned long long)prof_acc[i]);
+    }
+#endif
     if (ok && n > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n - 1) & 1, abort_flag, kWaitTmemFullTimeout));
       if (ok) {
@@ -462,6 +498,19 @@ static int attn_fwd_launch(const DptbAttnFwdArgs* a, cudaStream_t st) {
   dim3 grid(p.num_q_blocks, a->Hq, a->B);
   kern<<<grid, kAttnThreads, L::kTotal, st>>>(tmQ, tmK, tmV, p);
   return counted(1, (int)cudaGetLastError());
+}
+
+// Phase timers (see DPTB_ATTN_PROFILE): copies the 8 counters out and zeroes them; -5 when not compiled in.
+extern "C" int dptb_attn_fwd_profile_read(unsigned long long* out) {
+#ifdef DPTB_ATTN_PROFILE
+  int rc = (int)cudaMemcpyFromSymbol(out, g_attn_prof, sizeof(unsigned long long) * 8);
+  if (rc) return rc;
+  static unsigned long long zeros[8];
+  return (int)cudaMemcpyToSymbol(g_attn_prof, zeros, sizeof(zeros));
+#else
+  (void)out;
+  return kErrUnsupported;
+#endif
 }
 
 extern "C" int dptb_attn_fwd(const DptbAttnFwdArgs* a, void* stream) {

@@ -72,6 +72,25 @@ struct TpAr {
   int max_tiles;
   uint32_t* epoch;                          // local launch counter
   unsigned int* exit_counter;               // local, zero between launches
+  // mode 1 = reduce-scatter by rows (sequence-parallel output): rank r keeps rows [r * M / world, (r + 1) * M / world)
+  // of the sum in ITS output only (row 0 of that buffer = first row of the shard; bias / residual are indexed the same
+  // way).  The owner of a tile is then the rank that keeps its rows, and the row tiles are visited round-robin over
+  // the owners so that every rank's reductions are spread over the whole kernel.
+  int mode;
+  int rows_per_rank;
+};
+
+// All-gather prologue (column-parallel Linear on a row-sharded input): the A operand of row tile i is read by TMA from
+// the symmetric buffer of the rank that owns those rows (a plain, non-multicast tile load over NVLink; its own rows come
+// from local memory), after that rank's "shard ready" flag has reached the expected launch number.  world == 0: off.
+struct TpAg {
+  int world, rank;
+  int tiles_per_rank;                       // 128-row tiles per shard
+  const uint32_t* ready;                    // local flags [kMaxRanks], written by the peers' signal kernels
+  const uint32_t* epoch;                    // local word: the value ready[r] must have reached
+};
+struct TmapSet {
+  CUtensorMap m[kMaxRanks];
 };
 
 struct GemmParams {
@@ -100,7 +119,24 @@ struct GemmParams {
   float* ws;
   int* counters;
   TpAr ar;
+  TpAg ag;
 };
+
+// Row-tile index of work unit `tile` after the tensor-parallel re-orderings (identity otherwise).
+//   reduce-scatter: consecutive row tiles go to consecutive owners;
+//   all-gather:     every rank starts with its own shard and then walks the ring, so that at any moment the ranks pull
+//                   from different peers.
+__device__ __forceinline__ int tile_row_index(const GemmParams& p, int tile) {
+  int mi = tile % p.tiles_m;
+  if (p.ar.world > 0 && p.ar.mode == 1) {
+    const int tpr = p.tiles_m / p.ar.world;
+    mi = (mi % p.ar.world) * tpr + mi / p.ar.world;
+  } else if (p.ag.world > 0) {
+    const int tpr = p.ag.tiles_per_rank;
+    mi = ((mi / tpr + p.ag.rank) % p.ag.world) * tpr + mi % tpr;
+  }
+  return mi;
+}
 
 // ----------------------------------------------------------------------------- epilogue math
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -617,15 +653,19 @@ __device__ __forceinline__ void ar_reduce_block(const GemmParams& p, long long b
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] += bias8[e];
+    // Reduce-scatter: the shard's buffers start at the shard's first row.
+    const long long orow = p.ar.mode == 1 ? row - (long long)p.ar.rank * p.ar.rows_per_rank : row;
     if (p.residual) {
       float t[8];
-      unpack8(*reinterpret_cast<const uint4*>(p.residual + row * p.ldr + col), t);
+      unpack8(*reinterpret_cast<const uint4*>(p.residual + orow * p.ldr + col), t);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] += t[e];
     }
     const uint4 o = pack8(v);
-    const long long o_off = row * p.ldc + col;
-    if (p.ar.use_nvls) {
+    const long long o_off = orow * p.ldc + col;
+    if (p.ar.mode == 1) {
+      *reinterpret_cast<uint4*>(p.ar.out_peer[p.ar.rank] + o_off) = o;
+    } else if (p.ar.use_nvls) {
       multimem_st_bf16x8(p.ar.mc_out + o_off, o);
     } else {
       for (int r = 0; r < p.ar.world; ++r) st_cg_v4(p.ar.out_peer[r] + o_off, o);
@@ -650,9 +690,15 @@ struct GemmSmem {
   static_assert(kTotal <= 227 * 1024, "GEMM: shared memory budget");
 };
 
-template <bool A_MN, bool B_MN, int BN, int STAGES>
+// Extra kernel parameter of the all-gather variant: one tensor map per rank's shard of A.
+struct NoPeerMaps {};
+template <bool AG> struct PeerMaps { using type = NoPeerMaps; };
+template <> struct PeerMaps<true> { using type = TmapSet; };
+
+template <bool A_MN, bool B_MN, int BN, int STAGES, bool AG = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ typename PeerMaps<AG>::type peers, const GemmParams p) {
   using L = GemmSmem<BN, STAGES>;
   constexpr int TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
@@ -708,14 +754,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t issued = 0;
+      uint32_t ag_ready_mask = 0;
+      const uint32_t ag_epoch = AG ? *reinterpret_cast<const volatile uint32_t*>(p.ag.epoch) : 0u;
+      (void)ag_ready_mask;
+      (void)ag_epoch;
       DPTB_PROF_DECL(prof_wait);
       DPTB_PROF_BEGIN(prof_t_all);
       for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x) {
         const int tile = unit % num_tiles;
         const int kb0 = (unit / num_tiles) * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        const int m0 = (tile % p.tiles_m) * kBM;
+        const int mi = tile_row_index(p, tile);
+        const int m0 = mi * kBM;
         const int n0 = (tile / p.tiles_m) * BN;
+        const CUtensorMap* a_map = &tmA;
+        int a_row = m0;
+        if constexpr (AG) {
+          // Rows of another rank: wait (once per source, bounded) until its shard is published, then read it in place.
+          const int src = mi / p.ag.tiles_per_rank;
+          a_map = &peers.m[src];
+          a_row = (mi % p.ag.tiles_per_rank) * kBM;
+          if (!((ag_ready_mask >> src) & 1u)) {
+            if (src != p.ag.rank && !wait_flag_ge(p.ag.ready + src, ag_epoch)) {
+              *abort_flag = 1;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");   // the flag was read by the generic proxy, the tiles are not
+            ag_ready_mask |= 1u << src;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++issued) {
           const int s = issued % STAGES;
           const uint32_t ph = (issued / STAGES) & 1;
@@ -729,7 +796,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + j * 64, kb * kBK);
           } else {
-            tma_load_2d(a_dst, &tmA, &full_bar[s], kb * kBK, m0);
+            tma_load_2d(a_dst, a_map, &full_bar[s], kb * kBK, a_row);
           }
           if (B_MN) {
 #pragma unroll
@@ -880,7 +947,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
       const int tile = unit % num_tiles;
       const int split = unit / num_tiles;
-      const int m0 = (tile % p.tiles_m) * kBM;
+      const int m0 = tile_row_index(p, tile) * kBM;
       const int n0 = (tile / p.tiles_m) * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -920,7 +987,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);   // the issuer may start the next tile in this accumulator
         __threadfence_system();
         if (!epi_sync()) break;                          // every epilogue warp has written and fenced its blocks
-        const int owner = tile % p.ar.world;
+        const int owner = p.ar.mode == 1 ? m0 / p.ar.rows_per_rank : tile % p.ar.world;
         if (ew == 0 && lane == 0)
           st_release_sys(p.ar.flags_peer[owner] + (size_t)tile * kMaxRanks + p.ar.rank, ar_epoch);
         if (owner == p.ar.rank) {
@@ -1119,7 +1186,23 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmP
   }
   const int tiles = p.tiles_m * p.tiles_n * p.splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, NoPeerMaps{}, p);
+  return counted(1, (int)cudaGetLastError());
+}
+
+// All-gather variant: A (K-major) comes from every rank's shard, B is an nn.Linear weight (K-major).
+template <int BN, int STAGES>
+static int launch_tc_ag(const TmapSet& peers, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  auto kern = gemm_tc_kernel<false, false, BN, STAGES, true>;
+  static bool configured = false;
+  if (!configured) {
+    DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(peers.m[p.ag.rank], tmB, peers, p);
   return counted(1, (int)cudaGetLastError());
 }
 
@@ -1165,16 +1248,36 @@ struct DptbTpArArgs {
   void* flags_peer[kMaxRanks];
   void* epoch;
   void* exit_counter;
+  int mode;   // 0 = all-reduce into every rank's output, 1 = reduce-scatter by rows into this rank's output
+};
+// Peer-memory description of the all-gather prologue (see TpAg): every rank's shard of A, [rows_per_rank, lda] each.
+struct DptbTpAgArgs {
+  int world, rank;
+  long long rows_per_rank;
+  const void* a_peer[kMaxRanks];
+  const void* ready;   // local flag words [kMaxRanks], raised by dptb_tp_signal on the peers
+  const void* epoch;   // local word written by this rank's dptb_tp_signal: the value the flags must have reached
 };
 // 32-bit words of a flag array for `max_tiles` tiles.
 extern "C" long long dptb_tp_flag_words(int max_tiles) { return ((long long)max_tiles + 1) * kMaxRanks; }
 
-static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream_v) {
+static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTpAgArgs* ag, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (a->M <= 0 || a->N <= 0) return 0;
   if (a->K < 0) return kErrBadShape;
   GemmParams p;
   p.ar.world = 0;
+  p.ar.mode = 0;
+  p.ar.rows_per_rank = 0;
+  p.ag.world = 0;
+  const void* a_ptr = a->A;
+  if (ag) {
+    if (ar || ag->world < 1 || ag->world > kMaxRanks || ag->rank < 0 || ag->rank >= ag->world) return kErrBadShape;
+    if (a->trans_a || !a->trans_b || ag->rows_per_rank <= 0 || ag->rows_per_rank % kBM ||
+        ag->rows_per_rank * ag->world != a->M)
+      return kErrBadShape;
+    a_ptr = ag->a_peer[ag->rank];
+  }
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.C = a->C; p.ldc = a->ldc;
   p.bias = a->bias; p.bias_f32 = a->bias_f32;
@@ -1185,7 +1288,7 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream
   if (p.act >= 11 && !p.aux_in) return kErrBadShape;
 
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  const bool tc_ok = !a->force_simt && !a->a_f32 && !a->b_f32 && a->K > 0 && al16(a->A) && al16(a->B) &&
+  const bool tc_ok = !a->force_simt && !a->a_f32 && !a->b_f32 && a->K > 0 && al16(a_ptr) && al16(a->B) &&
                      (a->lda % 8 == 0) && (a->ldb % 8 == 0);
   p.vec_ok = al16(p.C) && (p.ldc % 8 == 0) && (!p.bias || al16(p.bias)) &&
              (!p.residual || (al16(p.residual) && p.ldr % 8 == 0)) &&
@@ -1197,7 +1300,9 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream
     if (!tc_ok || !p.vec_ok || (a->N % 8) || a->out_f32 || a->act || a->aux_out || a->aux_in || a->accumulate)
       return kErrUnsupported;
     if (ar->world < 1 || ar->world > kMaxRanks || ar->rank < 0 || ar->rank >= ar->world) return kErrBadShape;
+    if (ar->mode == 1 && (a->M % (ar->world * kBM))) return kErrBadShape;   // whole row tiles per shard
   }
+  if (ag && (!tc_ok || a->splits > 1)) return kErrUnsupported;
   if (!tc_ok) {
     p.tiles_m = p.tiles_n = p.num_kb = 0;
     p.splits = 1; p.kb_per_split = 0; p.ws = nullptr; p.counters = nullptr;
@@ -1232,7 +1337,7 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream
       const int tiles = tm * ((a->N + cand_bn - 1) / cand_bn);
       for (int sp = 1; sp <= 8; ++sp) {
         if (a->splits >= 1 && sp != a->splits) continue;
-        if (ar && sp > 1) break;
+        if ((ar || ag) && sp > 1) break;
         if (sp > 1) {
           if (!a->ws || !a->counters || tiles > a->num_counters) break;
           if ((long long)tiles * sp * cand_bn * kBM * 4 > a->ws_bytes) break;
@@ -1277,6 +1382,28 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream
     p.ar.max_tiles = ar->max_tiles;
     p.ar.epoch = static_cast<uint32_t*>(ar->epoch);
     p.ar.exit_counter = static_cast<unsigned int*>(ar->exit_counter);
+    p.ar.mode = ar->mode == 1 ? 1 : 0;
+    p.ar.rows_per_rank = a->M / ar->world;
+  }
+  if (ag) {
+    p.ag.world = ag->world;
+    p.ag.rank = ag->rank;
+    p.ag.tiles_per_rank = (int)(ag->rows_per_rank / kBM);
+    p.ag.ready = static_cast<const uint32_t*>(ag->ready);
+    p.ag.epoch = static_cast<const uint32_t*>(ag->epoch);
+    p.row_epi = (!p.out_f32 && p.vec_ok && !(p.bias && p.bias_f32)) ? 1 : 0;
+    TmapSet peers;
+    for (int r = 0; r < kMaxRanks; ++r) {
+      const int src = r < ag->world ? r : ag->rank;
+      if (!al16(ag->a_peer[src])) return kErrBadShape;
+      const int rc_a = encode_tmap_2d_bf16(&peers.m[r], ag->a_peer[src], (uint64_t)a->K, (uint64_t)ag->rows_per_rank,
+                                           (uint64_t)a->lda * 2, 64, kBM);
+      if (rc_a) return rc_a;
+    }
+    CUtensorMap tmBg;
+    const int rc_b = encode_tmap_2d_bf16(&tmBg, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb * 2, 64, (uint32_t)bn);
+    if (rc_b) return rc_b;
+    return bn == 256 ? launch_tc_ag<256, 4>(peers, tmBg, p, stream) : launch_tc_ag<128, 6>(peers, tmBg, p, stream);
   }
 
   CUtensorMap tmA, tmB;
@@ -1312,13 +1439,52 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream
 #undef DPTB_LAUNCH
 }
 
-extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) { return gemm_impl(a, nullptr, stream_v); }
+extern "C" int dptb_gemm(const DptbGemmArgs* a, void* stream_v) { return gemm_impl(a, nullptr, nullptr, stream_v); }
 // Row-parallel Linear of a tensor-parallel group in ONE kernel: tcgen05 GEMM of this rank's K-slice, then the sum over
 // ranks (+ bias, + residual) through NVLink peer memory, delivered to every rank's `out`.  Every rank must call it with
 // the same shapes; C of the argument block is ignored (the result goes to ar->out_peer / ar->mc_out with row stride ldc).
 extern "C" int dptb_gemm_allreduce(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream_v) {
   if (!ar) return kErrBadShape;
-  return gemm_impl(a, ar, stream_v);
+  return gemm_impl(a, ar, nullptr, stream_v);
+}
+// Column-parallel Linear on a row-sharded input in ONE kernel: row tile i of A is read by TMA straight from the
+// symmetric buffer of the rank that owns those rows, once that rank's dptb_tp_signal has published the shard; the
+// output [M, N] (this rank's slice of the features, all rows) is local.  A of the argument block is ignored.
+extern "C" int dptb_allgather_gemm(const DptbGemmArgs* a, const DptbTpAgArgs* ag, void* stream_v) {
+  if (!ag) return kErrBadShape;
+  return gemm_impl(a, nullptr, ag, stream_v);
+}
+
+// Publishes "this rank's shard is complete" to every peer: flag word [rank] of each peer's `ready` array and the local
+// launch counter both become *epoch + 1.  Runs after the kernel that wrote the shard, in stream order.
+struct DptbTpSignalArgs {
+  int world, rank;
+  void* ready_peer[kMaxRanks];   // every rank's flag array [kMaxRanks]
+  void* epoch;                   // local launch counter
+};
+namespace dptb {
+struct SignalParams {
+  int world, rank;
+  uint32_t* ready_peer[kMaxRanks];
+  uint32_t* epoch;
+};
+__global__ void tp_shard_signal_kernel(const SignalParams s) {
+  const uint32_t e = *reinterpret_cast<volatile uint32_t*>(s.epoch) + 1u;
+  __threadfence_system();   // the shard written by earlier kernels of this stream is visible system-wide first
+  if ((int)threadIdx.x < s.world) st_release_sys(s.ready_peer[threadIdx.x] + s.rank, e);
+  __syncwarp();
+  if (threadIdx.x == 0) *s.epoch = e;
+}
+}  // namespace dptb
+extern "C" int dptb_tp_signal(const DptbTpSignalArgs* a, void* stream_v) {
+  if (!a || a->world < 1 || a->world > kMaxRanks) return kErrBadShape;
+  SignalParams s;
+  s.world = a->world;
+  s.rank = a->rank;
+  for (int r = 0; r < kMaxRanks; ++r) s.ready_peer[r] = static_cast<uint32_t*>(a->ready_peer[r]);
+  s.epoch = static_cast<uint32_t*>(a->epoch);
+  tp_shard_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(s);
+  return counted(1, (int)cudaGetLastError());
 }
 
 // Status word access ------------------------------------------------------------------------------

@@ -33,7 +33,17 @@ class TpArArgs(ctypes.Structure):
                 ("partial", c_void_p), ("partial_elems", c_ll),
                 ("peer_partial", c_void_p * MAX_RANKS), ("mc_partial", c_void_p),
                 ("out_peer", c_void_p * MAX_RANKS), ("mc_out", c_void_p),
-                ("flags_peer", c_void_p * MAX_RANKS), ("epoch", c_void_p), ("exit_counter", c_void_p)]
+                ("flags_peer", c_void_p * MAX_RANKS), ("epoch", c_void_p), ("exit_counter", c_void_p),
+                ("mode", c_int)]
+
+
+class TpAgArgs(ctypes.Structure):
+    _fields_ = [("world", c_int), ("rank", c_int), ("rows_per_rank", c_ll),
+                ("a_peer", c_void_p * MAX_RANKS), ("ready", c_void_p), ("epoch", c_void_p)]
+
+
+class TpSignalArgs(ctypes.Structure):
+    _fields_ = [("world", c_int), ("rank", c_int), ("ready_peer", c_void_p * MAX_RANKS), ("epoch", c_void_p)]
 
 
 def _declare(lib):
@@ -41,6 +51,10 @@ def _declare(lib):
     lib.dptb_tp_flag_words.restype = c_ll
     lib.dptb_gemm_allreduce.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpArArgs), c_void_p]
     lib.dptb_gemm_allreduce.restype = c_int
+    lib.dptb_allgather_gemm.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpAgArgs), c_void_p]
+    lib.dptb_allgather_gemm.restype = c_int
+    lib.dptb_tp_signal.argtypes = [ctypes.POINTER(TpSignalArgs), c_void_p]
+    lib.dptb_tp_signal.restype = c_int
 
 
 def shard_range(total: int, rank: int, world: int):
@@ -86,6 +100,11 @@ class TpComm:
         self._h_flags = symm_mem.rendezvous(self.flags, group=gname)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         self.exit_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        # "shard ready" flags of the all-gather GEMM (one word per source rank) and this rank's publication counter
+        self.ready = symm_mem.empty(MAX_RANKS, dtype=torch.int32, device=dev)
+        self.ready.zero_()
+        self._h_ready = symm_mem.rendezvous(self.ready, group=gname)
+        self.ag_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         mc_ok = all(int(getattr(h, "multicast_ptr", 0) or 0) != 0 for h in [self._h_partial] + self._h_bufs)
         want = mc_ok if use_nvls is None else use_nvls
         env = os.environ.get("DPTB200_TP_NVLS")
@@ -106,7 +125,19 @@ class TpComm:
             a.mc_partial = int(self._h_partial.multicast_ptr) if self.use_nvls else None
             a.mc_out = int(self._h_bufs[i].multicast_ptr) if self.use_nvls else None
             a.epoch, a.exit_counter = self.epoch.data_ptr(), self.exit_counter.data_ptr()
+            a.mode = 0
             self._ar.append(a)
+        self._rs = []
+        for a in self._ar:
+            b = TpArArgs()
+            ctypes.memmove(ctypes.byref(b), ctypes.byref(a), ctypes.sizeof(TpArArgs))
+            b.mode = 1
+            self._rs.append(b)
+        self._sig = TpSignalArgs()
+        self._sig.world, self._sig.rank = self.world, self.rank
+        for r in range(MAX_RANKS):
+            self._sig.ready_peer[r] = int(self._h_ready.buffer_ptrs[r]) if r < self.world else None
+        self._sig.epoch = self.ag_epoch.data_ptr()
 
     def buffer(self, index: int, rows: int) -> torch.Tensor:
         """First ``rows`` rows of activation buffer ``index`` (this rank's copy)."""
@@ -115,7 +146,8 @@ class TpComm:
         return self.bufs[index][:rows]
 
     def gemm_allreduce(self, x: torch.Tensor, w_shard: torch.Tensor, out_index: int,
-                       residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                       scatter: bool = False) -> torch.Tensor:
         """``out = sum_over_ranks(x_r @ w_r^T) (+ bias) (+ residual)`` written into activation buffer ``out_index`` of
         EVERY rank.  ``x``: ``[M, K/world]`` bf16 (this rank's slice of the features), ``w_shard``: ``[N, K/world]``.
         ``residual`` (the same on all ranks) must not alias the output buffer."""
@@ -125,7 +157,12 @@ class TpComm:
             raise ValueError(f"gemm_allreduce: inner dimensions differ ({Kr} vs {w_shard.shape[1]})")
         if Nn != self.width:
             raise ValueError(f"gemm_allreduce: output width {Nn} != buffer width {self.width}")
-        out = self.buffer(out_index, M)
+        rows_out = M
+        if scatter:
+            if M % (self.world * 128):
+                raise ValueError(f"gemm_reduce_scatter: {M} rows do not split into whole 128-row tiles per rank")
+            rows_out = M // self.world
+        out = self.buffer(out_index, rows_out)
         if residual is not None and residual.data_ptr() == out.data_ptr():
             raise ValueError("gemm_allreduce: residual must live in a different buffer than the output")
         for t in (x, w_shard):
@@ -140,11 +177,56 @@ class TpComm:
         if bias is not None:
             g.bias, g.bias_f32 = bias.data_ptr(), int(bias.dtype == torch.float32)
         if residual is not None:
-            if residual.dtype != torch.bfloat16 or residual.shape[0] != M or residual.shape[1] < Nn:
+            if residual.dtype != torch.bfloat16 or residual.shape[0] != rows_out or residual.shape[1] < Nn:
                 raise ValueError("gemm_allreduce: residual has the wrong shape or dtype")
             g.residual, g.ldr = residual.data_ptr(), residual.stride(0)
-        N.check(self.lib.dptb_gemm_allreduce(ctypes.byref(g), ctypes.byref(self._ar[out_index]), N.stream_ptr()),
-                "gemm_allreduce")
+        args = self._rs[out_index] if scatter else self._ar[out_index]
+        N.check(self.lib.dptb_gemm_allreduce(ctypes.byref(g), ctypes.byref(args), N.stream_ptr()),
+                "gemm_reduce_scatter" if scatter else "gemm_allreduce")
+        return out
+
+    def gemm_reduce_scatter(self, x: torch.Tensor, w_shard: torch.Tensor, out_index: int,
+                            residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Sequence-parallel form of ``gemm_allreduce``: this rank keeps rows ``[rank * M / world, (rank + 1) * M /
+        world)`` of the sum, as the first ``M / world`` rows of its activation buffer ``out_index``; ``residual`` is
+        this rank's ``[M / world, N]`` shard."""
+        return self.gemm_allreduce(x, w_shard, out_index, residual=residual, bias=bias, scatter=True)
+
+    def publish_shard(self) -> None:
+        """Tell every peer that this rank's row shard (written by kernels launched so far on the current stream) is
+        complete.  Every rank calls it once before each ``allgather_gemm``."""
+        N.check(self.lib.dptb_tp_signal(ctypes.byref(self._sig), N.stream_ptr()), "tp_signal")
+
+    def allgather_gemm(self, in_index: int, rows_per_rank: int, w_shard: torch.Tensor, out: torch.Tensor,
+                       bias: Optional[torch.Tensor] = None, act=None) -> torch.Tensor:
+        """``out[world * rows_per_rank, N] = concat_over_ranks(shard_r) @ w_shard^T``: column-parallel Linear whose
+        input is row-sharded.  Rank r's shard is the first ``rows_per_rank`` rows of ITS activation buffer
+        ``in_index``; the kernel reads the peers' shards in place over NVLink (``publish_shard`` first)."""
+        if rows_per_rank % 128 or rows_per_rank > self.max_rows:
+            raise ValueError("allgather_gemm: rows_per_rank must be a multiple of 128 within the buffer")
+        Nn, K = w_shard.shape
+        if K != self.width:
+            raise ValueError(f"allgather_gemm: inner dimension {K} != buffer width {self.width}")
+        M = rows_per_rank * self.world
+        if out.shape[0] != M or out.shape[1] < Nn or out.dtype != torch.bfloat16 or out.stride(-1) != 1:
+            raise ValueError("allgather_gemm: output must be bf16 [world * rows_per_rank, >= N]")
+        g = N.GemmArgs()
+        src = self.bufs[in_index]
+        g.A, g.B, g.C = src.data_ptr(), w_shard.data_ptr(), out.data_ptr()
+        g.lda, g.ldb, g.ldc = src.stride(0), w_shard.stride(0), out.stride(0)
+        g.M, g.N, g.K = M, Nn, K
+        g.trans_a, g.trans_b = 0, 1
+        g.alpha, g.splits = 1.0, 1
+        if bias is not None:
+            g.bias, g.bias_f32 = bias.data_ptr(), int(bias.dtype == torch.float32)
+        if act is not None:
+            g.act = K.ACT_CODES[act]
+        ag = TpAgArgs()
+        ag.world, ag.rank, ag.rows_per_rank = self.world, self.rank, rows_per_rank
+        for r in range(MAX_RANKS):
+            ag.a_peer[r] = int(self._h_bufs[in_index].buffer_ptrs[r]) if r < self.world else None
+        ag.ready, ag.epoch = self.ready.data_ptr(), self.ag_epoch.data_ptr()
+        N.check(self.lib.dptb_allgather_gemm(ctypes.byref(g), ctypes.byref(ag), N.stream_ptr()), "allgather_gemm")
         return out
 
 

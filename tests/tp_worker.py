@@ -44,6 +44,41 @@ def check_comm(comm, rank, world, tag):
         print(f"tp_worker {tag}: fused GEMM + all-reduce matches (nvls={comm.use_nvls})")
 
 
+def check_sequence_parallel(comm, rank, world, tag):
+    """Row-parallel GEMM + reduce-scatter, then (after publishing the shard) all-gather + column-parallel GEMM: the
+    pair must equal the un-sharded  (x @ w1^T + res) @ w2^T  with the intermediate rounded to bf16."""
+    K1, D, N2 = 1024, comm.width, 768
+    lo, hi = shard_range(K1, rank, world)
+    n_lo, n_hi = shard_range(N2, rank, world)
+    for trial, rows_per_rank in enumerate((128, 256, 512)):
+        M = rows_per_rank * world
+        g = torch.Generator(device="cuda").manual_seed(100 + trial)
+        x_full = (torch.randn(M, K1, device="cuda", generator=g) * 0.5).bfloat16()
+        w1 = (torch.randn(D, K1, device="cuda", generator=g) * 0.05).bfloat16()
+        res = torch.randn(M, D, device="cuda", generator=g).bfloat16()
+        w2 = (torch.randn(N2, D, device="cuda", generator=g) * 0.05).bfloat16()
+        bias2 = torch.randn(N2, device="cuda", generator=g).bfloat16()
+        x, w1s = x_full[:, lo:hi].contiguous(), w1[:, lo:hi].contiguous()
+        w2s, b2s = w2[n_lo:n_hi].contiguous(), bias2[n_lo:n_hi].contiguous()
+        res_shard = res[rank * rows_per_rank:(rank + 1) * rows_per_rank].contiguous()
+        out = torch.empty(M, n_hi - n_lo, dtype=torch.bfloat16, device="cuda")
+        for rep in range(3):
+            shard = comm.gemm_reduce_scatter(x, w1s, 0, residual=res_shard)
+            comm.publish_shard()
+            comm.allgather_gemm(0, rows_per_rank, w2s, out, bias=b2s)
+            # the next reduce-scatter overwrites buffer 0: its end barrier orders it after every rank's all-gather
+        torch.cuda.synchronize()
+        _native.raise_on_device_error()
+        mid = reference_row_parallel(x_full, w1, residual=res)
+        err = (shard.float() - mid[rank * rows_per_rank:(rank + 1) * rows_per_rank]).abs().max().item()
+        assert err <= 0.02 * mid.abs().max().item() + 0.05, f"{tag} reduce-scatter rows/rank={rows_per_rank}: err {err}"
+        want = (mid.bfloat16().float() @ w2.float().t() + bias2.float())[:, n_lo:n_hi]
+        err = (out.float() - want).abs().max().item()
+        assert err <= 0.03 * want.abs().max().item() + 0.05, f"{tag} all-gather GEMM rows/rank={rows_per_rank}: err {err}"
+    if rank == 0:
+        print(f"tp_worker {tag}: reduce-scatter GEMM and all-gather GEMM match")
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -53,6 +88,8 @@ def main():
     if mode == "p2p":
         assert not comm.use_nvls
     check_comm(comm, rank, world, mode)
+    big = TpComm(max_rows=512 * world, width=512, use_nvls=False if mode == "p2p" else None)
+    check_sequence_parallel(big, rank, world, mode)
     torch.cuda.synchronize()
     dist.barrier()
     if rank == 0:
