@@ -172,3 +172,18 @@ def test_moe_language_model_reference_defaults_and_benchmark_options():
         first = first or float(loss)
     assert float(loss) < first and float(b.aux_loss()) > 0
     b.update_routing_bias()
+
+
+def test_tiny_char_gpt_recipe_end_to_end():
+    """The smallest end-to-end workload (train with warm-up / cosine / clipping, DPTC round trip, cached greedy
+    generation) runs and is self-consistent on the CPU."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from benchmarks.tiny_gpt_cpu import run_ours
+    res = run_ours(24)
+    assert res["checkpoint_round_trip"] and res["generate_matches_after_reload"] and res["cache_matches_no_cache"]
+    assert res["checkpoint_bytes"] > 4 * 65 * 64
+    # cached generation stops when the context (32 positions) is full
+    assert 32 <= len(res["generated"]) <= 3 + 32 and all(0 <= t < 65 for t in res["generated"])
+    assert abs(res["loss_first"] - 4.17) < 0.2          # ln(65) for random tokens
