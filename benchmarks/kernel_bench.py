@@ -83,6 +83,12 @@ def build_cases(dev, want=()):
     gemm_case("gemm_qkv_wgrad", 3 * D, D, M, True, False)
     gemm_case("gemm_proj_wgrad", D, D, M, True, False)
     gemm_case("gemm_8192", 8192, 8192, 8192, False, True)
+    # decode-sized rows: the per-GPU projections of a Llama-3-8B layer at TP = 8, batch 32 (weight streaming)
+    gemm_case("gemm_dec_qkv", 32, 768, 4096, False, True)
+    gemm_case("gemm_dec_wo", 32, 4096, 512, False, True)
+    gemm_case("gemm_dec_gateup", 32, 3584, 4096, False, True)
+    gemm_case("gemm_dec_down", 32, 4096, 1792, False, True)
+    gemm_case("gemm_dec_head", 32, 16032, 4096, False, True)
 
     if on("norm"):
       _, mean, rstd = K.layernorm_fwd(x, gamma, beta, 1e-5)

@@ -16,6 +16,7 @@
 //               works on the next tile in the other accumulator.
 #include <cuda_bf16.h>
 
+#include "common/gemm_args.h"
 #include "common/host.h"
 #include "common/peer.cuh"
 #include "common/ptx.cuh"
@@ -1210,46 +1211,6 @@ static int launch_tc_ag(const TmapSet& peers, const CUtensorMap& tmB, const Gemm
 
 using namespace dptb;
 
-// Argument block of dptb_gemm (mirrored by a ctypes.Structure in Python).
-struct DptbGemmArgs {
-  const void* A;
-  const void* B;
-  void* C;
-  const void* bias;
-  const void* residual;
-  void* aux_out;
-  const void* aux_in;
-  long long lda, ldb, ldc, ldr, ld_aux_out, ld_aux_in;
-  int M, N, K;
-  int trans_a;   // 0: A stored [M, K] row-major; 1: A stored [K, M] row-major
-  int trans_b;   // 0: B stored [K, N] row-major; 1: B stored [N, K] row-major (nn.Linear weight)
-  int a_f32, b_f32;  // inputs are fp32 (SIMT path only)
-  int bias_f32, out_f32, accumulate, act;
-  float alpha;
-  int force_simt;
-  int bn;        // 0 = choose, else 128 or 256
-  int splits;    // split-K factor: 0 = choose, 1 = off
-  void* ws;      // fp32 scratch for split-K partial tiles (may be null: no split-K)
-  long long ws_bytes;
-  int* counters; // zero-initialised per-tile arrival counters (they return to zero after every launch)
-  int num_counters;
-};
-
-// Peer-memory description of the all-reduce epilogue (see TpAr).  `partial_elems` / `max_tiles` are capacities that
-// the launcher checks against the tiling it picks.
-struct DptbTpArArgs {
-  int world, rank, use_nvls, max_tiles;
-  void* partial;
-  long long partial_elems;
-  const void* peer_partial[kMaxRanks];
-  const void* mc_partial;
-  void* out_peer[kMaxRanks];
-  void* mc_out;
-  void* flags_peer[kMaxRanks];
-  void* epoch;
-  void* exit_counter;
-  int mode;   // 0 = all-reduce into every rank's output, 1 = reduce-scatter by rows into this rank's output
-};
 // Peer-memory description of the all-gather prologue (see TpAg): every rank's shard of A, [rows_per_rank, lda] each.
 struct DptbTpAgArgs {
   int world, rank;

@@ -129,6 +129,7 @@ def _declare(lib: ctypes.CDLL) -> None:
 
     P, I, L, F = c_void_p, c_int, c_ll, c_float
     sig("dptb_gemm", ctypes.POINTER(GemmArgs), P)
+    sig("dptb_gemm_skinny", ctypes.POINTER(GemmArgs), P, P)
     sig("dptb_status_read", ctypes.POINTER(c_int * 4))
     sig("dptb_status_clear")
     sig("dptb_layernorm_fwd", P, P, P, P, P, P, L, I, F, I, P)

@@ -6,6 +6,7 @@ parallel layer share.  Every wrapper validates shapes on the host and raises on 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -25,6 +26,9 @@ def _lead(t: torch.Tensor) -> int:
 
 _SPLITK_WS = {}
 SPLITK_WS_BYTES = 64 << 20
+SKINNY_MAX_ROWS = 64      # rows up to which x @ W^T takes the weight-streaming kernel (csrc/gemm_skinny.cu)
+_SKINNY_ON = os.environ.get("DPTB200_SKINNY_GEMM", "1") != "0"
+ERR_UNSUPPORTED = -5
 SPLITK_COUNTERS = 4096
 
 
@@ -107,6 +111,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: bool =
         ws, counters = splitk_workspace(a.device)
         args.ws, args.ws_bytes = ws.data_ptr(), ws.numel()
         args.counters, args.num_counters = counters.data_ptr(), counters.numel()
+    if M <= SKINNY_MAX_ROWS and trans_b and not trans_a and not force_simt and bn == 0 and _SKINNY_ON:
+        # decode-sized rows: the weight-streaming kernel (declines, with "unsupported", what it does not cover)
+        rc = lib.dptb_gemm_skinny(ctypes.byref(args), None, N.stream_ptr())
+        if rc != ERR_UNSUPPORTED:
+            N.check(rc, "gemm_skinny")
+            return out
     N.check(lib.dptb_gemm(ctypes.byref(args), N.stream_ptr()), "gemm")
     return out
 

@@ -55,6 +55,8 @@ def _declare(lib):
     lib.dptb_allgather_gemm.restype = c_int
     lib.dptb_tp_signal.argtypes = [ctypes.POINTER(TpSignalArgs), c_void_p]
     lib.dptb_tp_signal.restype = c_int
+    lib.dptb_gemm_skinny.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpArArgs), c_void_p]
+    lib.dptb_gemm_skinny.restype = c_int
 
 
 def shard_range(total: int, rank: int, world: int):
@@ -181,6 +183,17 @@ class TpComm:
                 raise ValueError("gemm_allreduce: residual has the wrong shape or dtype")
             g.residual, g.ldr = residual.data_ptr(), residual.stride(0)
         args = self._rs[out_index] if scatter else self._ar[out_index]
+        if M <= K.SKINNY_MAX_ROWS and not scatter and K._SKINNY_ON:
+            # decode-sized rows: the weight-streaming kernel with the same fused all-reduce (split-K needs scratch)
+            ws, counters = K.splitk_workspace(x.device)
+            g.splits = 0
+            g.ws, g.ws_bytes = ws.data_ptr(), ws.numel()
+            g.counters, g.num_counters = counters.data_ptr(), counters.numel()
+            rc = self.lib.dptb_gemm_skinny(ctypes.byref(g), ctypes.byref(args), N.stream_ptr())
+            if rc != K.ERR_UNSUPPORTED:
+                N.check(rc, "gemm_skinny_allreduce")
+                return out
+            g.splits = 1
         N.check(self.lib.dptb_gemm_allreduce(ctypes.byref(g), ctypes.byref(args), N.stream_ptr()),
                 "gemm_reduce_scatter" if scatter else "gemm_allreduce")
         return out

@@ -94,6 +94,26 @@ def test_gemm_epilogue_in_place_residual_accumulate_and_padding():
     assert _rel_err(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize("M", [1, 7, 32, 33, 64])
+@pytest.mark.parametrize("N,Kd", [(768, 4096), (200, 264), (4096, 512), (16032, 1024)])
+@pytest.mark.parametrize("extras", [False, True])
+def test_gemm_skinny_rows(M, N, Kd, extras):
+    """Decode-sized rows take the weight-streaming kernel (operands swapped on the tensor core, K split over the SMs)."""
+    x, w = _mk((M, Kd), seed=31), _mk((N, Kd), scale=0.05, seed=32)
+    bias = _mk((N,), seed=33) if extras else None
+    res = _mk((M, N), seed=34) if extras else None
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.gemm(x, w, out, trans_b=True, bias=bias, residual=res)
+    ref = x.float() @ w.float().t()
+    if extras:
+        ref = ref + bias.float() + res.float()
+    assert torch.isfinite(out.float()).all()
+    assert _rel_err(out, ref) < 1e-2
+    again = torch.empty_like(out)
+    K.gemm(x, w, again, trans_b=True, bias=bias, residual=res)
+    assert torch.equal(out, again)          # split-K partials are summed in a fixed order
+
+
 @pytest.mark.parametrize("act", ["relu", "gelu_tanh", "quick_gelu", "silu"])
 def test_gemm_epilogue_act_backward(act):
     M, N, Kd = 256, 256, 128
