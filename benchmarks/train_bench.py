@@ -186,7 +186,7 @@ class _TorchMoEBlock(torch.nn.Module):
         back = torch.empty_like(back_in)
         dist.all_to_all_single(back, back_in)
         gathered = back[pos.clamp(max=E * C - 1)] * (w.reshape(-1, 1) * keep[:, None]).to(back.dtype)
-        y = x.new_zeros(T, d).index_add_(0, src_rows, gathered)
+        y = x.new_zeros(T, d).index_add_(0, src_rows, gathered.to(x.dtype))
         f = onehot.float().mean(0)
         return y, m["aux"] * E * (f * probs.mean(0)).sum()
 
@@ -246,14 +246,16 @@ def moe_torch(args, rank, world):
             loss = torch.nn.functional.cross_entropy(logits.float().view(-1, m["vocab"]), t[:, 1:].reshape(-1)) + aux
         loss.backward()
         if world > 1:
-            flat = torch.cat([p.grad.reshape(-1) for p in shared])
+            live = [p for p in shared if p.grad is not None]
+            flat = torch.cat([p.grad.reshape(-1) for p in live])
             dist.all_reduce(flat, op=dist.ReduceOp.AVG)
             off = 0
-            for p in shared:
+            for p in live:
                 p.grad.copy_(flat[off:off + p.numel()].view_as(p))
                 off += p.numel()
             for p in expert:
-                p.grad.div_(world)
+                if p.grad is not None:
+                    p.grad.div_(world)
         torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
         opt.step()
         return loss

@@ -101,7 +101,9 @@ class LinearFn(torch.autograd.Function):
         ctx.w, ctx.b, ctx.act = w, b, act
         ctx.has_res = residual is not None
         ctx.xshape = x.shape
-        return out.view(*x.shape[:-1], Nn)
+        # A 2-D input gets the fresh buffer itself, not a view of it: in-place consumers (the rotary embedding of the
+        # fused QKV output) may not modify a view created inside a custom Function.
+        return out if x.dim() == 2 else out.view(*x.shape[:-1], Nn)
 
     @staticmethod
     def backward(ctx, dy):

@@ -89,3 +89,30 @@ def test_training_step_on_arena_reduces_loss_and_checkpoint_round_trips():
         b = other(x[:1]).float()
     assert float((a - b).abs().max()) < 1e-2
     assert dp.Checkpoint.save_bytes(other)[:12] == blob[:12]
+
+
+def test_llama_loss_and_grads_match_cpu_reference():
+    """Training path of the Llama family on the GPU: RMSNorm, in-place rotary embedding of the fused QKV output,
+    grouped-query flash attention, SwiGLU, against the fp32 CPU reference of the same model."""
+    from dart_pytorch_b200.models.llama import Llama, LlamaConfig
+
+    def make():
+        return Llama(LlamaConfig(vocab_size=320, max_ctx=256, embed_dim=256, num_layers=2, num_heads=4, num_kv_heads=2,
+                                 ffn_dim=512, rope_base=10000.0, tie_weights=False, seed=5, init_std=0.02))
+    cpu, gpu = make(), make()
+    gpu.to("cuda", torch.bfloat16)
+    for b, a in zip(cpu.parameters(), gpu.parameters()):
+        b.data.copy_(a.data.float().cpu())
+    g = torch.Generator().manual_seed(2)
+    x = torch.randint(0, 320, (2, 256), generator=g)
+    y = torch.roll(x, -1, 1)
+    lc = cpu.loss(x, y)
+    lc.backward()
+    lg = gpu.loss(x.cuda(), y.cuda())
+    lg.backward()
+    assert abs(float(lc) - float(lg)) < 3e-2
+    for pc, pg in zip(cpu.parameters(), gpu.parameters()):
+        assert pg.grad is not None
+        num = (pg.grad.float().cpu() - pc.grad).norm()
+        den = pc.grad.norm() + 1e-8
+        assert float(num / den) < 8e-2, (tuple(pc.shape), float(num / den))
