@@ -112,7 +112,8 @@ def main():
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--new", type=int, default=256)
-    ap.add_argument("--prefill-rows", type=int, default=8192)
+    ap.add_argument("--prefill-rows", type=int, default=65536,
+                    help="token rows per prefill call (whole sequences); both implementations use the same chunking")
     ap.add_argument("--prefill-reps", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()

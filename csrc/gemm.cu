@@ -7,13 +7,14 @@
 // row-broadcast-add / activation kernels around it (reference: lib/native/src/kernels/matmul.cuh:27-63,
 // lib/native/src/kernels/transpose.cuh:12-29, lib/native/src/kernels/elementwise.cuh:64-73).
 //
-// Structure of the tensor-core kernel (one persistent CTA per SM, 192 threads):
+// Structure of the tensor-core kernel (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: one elected lane streams 128xBK / BNxBK tiles into a STAGES-deep ring.
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128, N=BN, K=16) into one of two
 //               TMEM accumulators; tcgen05.commit releases smem stages and publishes accumulators.
-//   warps 2-5   epilogue: tcgen05.ld of the finished accumulator (one row per thread), bias /
-//               activation / residual / accumulate, bf16 or fp32 stores, while the issuer already
-//               works on the next tile in the other accumulator.
+//   warps 2-9   epilogue (two warps per TMEM lane quarter, alternating 64-column blocks): tcgen05.ld of the
+//               finished accumulator (one row per thread), bias / activation / residual / accumulate in
+//               registers, bf16 or fp32 stores, while the issuer already works on the next tile in the
+//               other accumulator.
 #include <cuda_bf16.h>
 
 #include "common/gemm_args.h"
@@ -193,90 +194,6 @@ __device__ __forceinline__ void epilogue_scalar(const GemmParams& p, long long r
   } else {
     __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
     *c = __float2bfloat16(p.accumulate ? __bfloat162float(*c) + v : v);
-  }
-}
-
-__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&out)[32]) {
-  const uint4* s4 = reinterpret_cast<const uint4*>(src);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 u = s4[i];
-    float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-    out[i * 8 + 0] = a.x; out[i * 8 + 1] = a.y; out[i * 8 + 2] = b.x; out[i * 8 + 3] = b.y;
-    out[i * 8 + 4] = c.x; out[i * 8 + 5] = c.y; out[i * 8 + 6] = d.x; out[i * 8 + 7] = d.y;
-  }
-}
-__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32]) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint4 u;
-    u.x = pack_bf16x2(v[i * 8 + 0], v[i * 8 + 1]);
-    u.y = pack_bf16x2(v[i * 8 + 2], v[i * 8 + 3]);
-    u.z = pack_bf16x2(v[i * 8 + 4], v[i * 8 + 5]);
-    u.w = pack_bf16x2(v[i * 8 + 6], v[i * 8 + 7]);
-    d4[i] = u;
-  }
-}
-
-// 32 consecutive columns of one row, all in range and 16-byte aligned.
-__device__ __forceinline__ void epilogue_vec32(const GemmParams& p, long long row, long long col, float (&v)[32]) {
-  if (p.alpha != 1.0f) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
-  }
-  if (p.bias) {
-    if (p.bias_f32) {
-      const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float4 b = __ldg(b4 + i);
-        v[i * 4 + 0] += b.x; v[i * 4 + 1] += b.y; v[i * 4 + 2] += b.z; v[i * 4 + 3] += b.w;
-      }
-    } else {
-      float b[32];
-      load_bf16x32(static_cast<const __nv_bfloat16*>(p.bias) + col, b);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] += b[i];
-    }
-  }
-  if (p.aux_out) store_bf16x32(p.aux_out + row * p.ld_aux_out + col, v);
-  if (p.act >= 1 && p.act <= 4) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = act_fwd(p.act, v[i]);
-  }
-  if (p.act >= 11) {
-    float pre[32];
-    load_bf16x32(p.aux_in + row * p.ld_aux_in + col, pre);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] *= act_bwd(p.act, pre[i]);
-  }
-  if (p.residual) {
-    float r[32];
-    load_bf16x32(p.residual + row * p.ldr + col, r);
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] += r[i];
-  }
-  if (p.out_f32) {
-    float4* c4 = reinterpret_cast<float4*>(static_cast<float*>(p.C) + row * p.ldc + col);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float4 o = make_float4(v[i * 4 + 0], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
-      if (p.accumulate) {
-        float4 c = c4[i];
-        o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
-      }
-      c4[i] = o;
-    }
-  } else {
-    __nv_bfloat16* c = static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col;
-    if (p.accumulate) {
-      float old[32];
-      load_bf16x32(c, old);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] += old[i];
-    }
-    store_bf16x32(c, v);
   }
 }
 
@@ -633,25 +550,10 @@ __device__ __forceinline__ void ar_reduce_block(const GemmParams& p, long long b
       bias8[e] = p.bias_f32 ? __ldg(static_cast<const float*>(p.bias) + col + e)
                             : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + e]);
   }
-#pragma unroll 2
-  for (int it = 0; it < 8; ++it) {
-    const int rl = it * 4 + rg;
+  // Remote loads have microseconds of latency: all loads of a group of rows are issued before the first one is used
+  // (8 rows at a time through the switch, 2 rows x all ranks at a time over peer pointers).
+  auto finish = [&](int rl, float (&v)[8]) {
     const long long row = row0 + rl;
-    if (row >= p.M) continue;
-    const long long off = blk_off + rl * 64 + cg * 8;
-    float v[8];
-    if (p.ar.use_nvls) {
-      unpack8(multimem_ld_reduce_bf16x8(p.ar.mc_partial + off), v);
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = 0.0f;
-      for (int r = 0; r < p.ar.world; ++r) {
-        float t[8];
-        unpack8(ld_cg_v4(p.ar.peer_partial[r] + off), t);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] += t[e];
-      }
-    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] += bias8[e];
     // Reduce-scatter: the shard's buffers start at the shard's first row.
@@ -670,6 +572,51 @@ __device__ __forceinline__ void ar_reduce_block(const GemmParams& p, long long b
       multimem_st_bf16x8(p.ar.mc_out + o_off, o);
     } else {
       for (int r = 0; r < p.ar.world; ++r) st_cg_v4(p.ar.out_peer[r] + o_off, o);
+    }
+  };
+  if (p.ar.use_nvls) {
+    uint4 raw[8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int rl = it * 4 + rg;
+      raw[it] = make_uint4(0, 0, 0, 0);
+      if (row0 + rl < p.M) raw[it] = multimem_ld_reduce_bf16x8(p.ar.mc_partial + blk_off + rl * 64 + cg * 8);
+    }
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int rl = it * 4 + rg;
+      if (row0 + rl >= p.M) continue;
+      float v[8];
+      unpack8(raw[it], v);
+      finish(rl, v);
+    }
+  } else {
+#pragma unroll 1
+    for (int it0 = 0; it0 < 8; it0 += 2) {
+      uint4 raw[2][kMaxRanks];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int rl = (it0 + j) * 4 + rg;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          raw[j][r] = make_uint4(0, 0, 0, 0);
+          if (r < p.ar.world && row0 + rl < p.M) raw[j][r] = ld_cg_v4(p.ar.peer_partial[r] + blk_off + rl * 64 + cg * 8);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int rl = (it0 + j) * 4 + rg;
+        if (row0 + rl >= p.M) continue;
+        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {   // fixed rank order; absent ranks contribute zeros
+          float t[8];
+          unpack8(raw[j][r], t);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] += t[e];
+        }
+        finish(rl, v);
+      }
     }
   }
 }
@@ -914,6 +861,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     };
     uint32_t* bias_s = reinterpret_cast<uint32_t*>(smem + L::kBiasOff) + ew * 32;
+    // Tiles this rank owns whose cross-rank reduction is still outstanding (all-reduce epilogue).
+    int ar_tile[2] = {0, 0};
+    int ar_pending = 0;
+    auto ar_reduce_tile = [&](int t) -> bool {
+      bool got = true;
+      if (lane < p.ar.world) got = wait_flag_ge(p.ar.flags_peer[p.ar.rank] + (size_t)t * kMaxRanks + lane, ar_epoch);
+      if (!__all_sync(0xffffffffu, got)) {
+        *abort_flag = 1;
+        return false;
+      }
+      const int tm0 = tile_row_index(p, t) * kBM;
+      const int tn0 = (t / p.tiles_m) * BN;
+#pragma unroll 1
+      for (int c = half; c < BN / 64; c += 2) {
+        const long long col0 = (long long)tn0 + c * 64;
+        if (col0 >= p.N) break;
+        ar_reduce_block(p, (long long)t * (BN * kBM) + (long long)c * (64 * kBM) + (long long)(q * 32) * 64,
+                        (long long)tm0 + q * 32, col0, lane);
+      }
+      return true;
+    };
     // Bounded barrier over the epilogue warps (a hardware named barrier could not give up).
     auto epi_sync = [&]() -> bool {
       __syncwarp();
@@ -959,7 +927,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       if (p.ar.world > 0) {
-        // Partial tile -> this rank's partial buffer; flag the owner; the owner reduces and broadcasts.
+        // Partial tile -> this rank's partial buffer (each thread writes its row's 128 bytes of a 64-column block as
+        // whole sectors); flag the owner.  The CTA-wide barrier orders every warp's stores before the one
+        // release-at-system-scope store of the flag (release is cumulative over that synchronisation).
         __nv_bfloat16* ptile = p.ar.partial + (size_t)tile * (BN * kBM);
 #pragma unroll 1
         for (int c = half; c < BN / 64; c += 2) {
@@ -968,44 +938,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tmem_ld_32x32(t_row + c * 64, r0);
           tmem_ld_32x32(t_row + c * 64 + 32, r1);
           tmem_ld_wait();
-          uint8_t* srow = stage + lane * 128;
+          uint4 o[8];
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             const uint32_t* src = g < 4 ? &r0[g * 8] : &r1[(g - 4) * 8];
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
-            u.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
-            u.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
-            u.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
-            *reinterpret_cast<uint4*>(srow + ((g ^ (lane & 7)) << 4)) = u;
+            o[g].x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
+            o[g].y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
+            o[g].z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
+            o[g].w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
           }
-          __syncwarp();
-          ar_store_partial(p, stage, ptile + (size_t)c * (64 * kBM) + (size_t)(q * 32) * 64, row0, lane);
-          __syncwarp();
+          if (row0 + lane < p.M)
+            st_row64(ptile + (size_t)c * (64 * kBM) + (size_t)(q * 32 + lane) * 64, true, o);
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);   // the issuer may start the next tile in this accumulator
-        __threadfence_system();
-        if (!epi_sync()) break;                          // every epilogue warp has written and fenced its blocks
+        if (!epi_sync()) break;                          // every epilogue warp has written its blocks
         const int owner = p.ar.mode == 1 ? m0 / p.ar.rows_per_rank : tile % p.ar.world;
         if (ew == 0 && lane == 0)
           st_release_sys(p.ar.flags_peer[owner] + (size_t)tile * kMaxRanks + p.ar.rank, ar_epoch);
+        // The owner's reduction of a tile is deferred until two more tiles have been stored: by then the other
+        // ranks' partials of that tile have usually arrived, so the wait does not stall the pipeline.
         if (owner == p.ar.rank) {
-          bool ok = true;
-          if (lane < p.ar.world)
-            ok = wait_flag_ge(p.ar.flags_peer[p.ar.rank] + (size_t)tile * kMaxRanks + lane, ar_epoch);
-          if (!__all_sync(0xffffffffu, ok)) {
-            *abort_flag = 1;
-            break;
+          if (ar_pending == 2) {
+            if (!ar_reduce_tile(ar_tile[0])) break;
+            ar_tile[0] = ar_tile[1];
+            ar_pending = 1;
           }
-#pragma unroll 1
-          for (int c = half; c < BN / 64; c += 2) {
-            const long long col0 = (long long)n0 + c * 64;
-            if (col0 >= p.N) break;
-            ar_reduce_block(p, (long long)tile * (BN * kBM) + (long long)c * (64 * kBM) + (long long)(q * 32) * 64, row0,
-                            col0, lane);
-          }
+          ar_tile[ar_pending++] = tile;
         }
       } else if (p.splits == 1) {
 #pragma unroll 1
@@ -1104,6 +1064,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!epi_sync()) break;  // epi_last may be rewritten only after every warp has read it
       }
     }
+    for (int i = 0; i < ar_pending && !*abort_flag; ++i)
+      if (!ar_reduce_tile(ar_tile[i])) break;
 #ifdef DPTB_GEMM_PROFILE
     if (ew == 0 && lane == 0) {
       DPTB_PROF_STORE(5, prof_wait_acc);
