@@ -484,11 +484,36 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
     for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
     if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
   }
-  if (p.act >= 1 && p.act <= 4) {
+  if (p.act == 2) {
+    // GELU (tanh form), the one activation on the training hot path, outside the per-group dispatch: five
+    // multiply-adds and one tanh.approx per element, all 64 elements independent.
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      const float x = v[i];
+      const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);   // 0.79788456 (x + 0.044715 x^3)
+      const float hx = 0.5f * x;
+      v[i] = fmaf(hx, tanh_fast(u), hx);
+    }
+  } else if (p.act >= 1 && p.act <= 4) {
 #pragma unroll
     for (int g = 0; g < 8; ++g) apply_act8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]));
   }
-  if (p.act >= 11) {
+  if (p.act == 12) {
+    // GELU (tanh form) derivative, outside the per-group dispatch like the forward:
+    //   d = 0.5 (1 + t) + 0.5 x (1 - t^2) (0.79788456 + 0.10703222 x^2),  t = tanh(0.79788456 (x + 0.044715 x^3))
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float x[8];
+      unpack8(in.v[g], x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xx = x[e] * x[e];
+        const float t = tanh_fast(x[e] * fmaf(xx, 0.0356774081f, 0.7978845608f));
+        const float s = x[e] * fmaf(xx, 0.1070322243f, 0.7978845608f);
+        v[g * 8 + e] *= 0.5f * (1.0f + t + s * fmaf(-t, t, 1.0f));
+      }
+    }
+  } else if (p.act >= 11) {
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
       float x[8];
@@ -525,18 +550,6 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
 }
 
 // ----------------------------------------------------------------------------- all-reduce epilogue helpers
-// Copy the staged 32 x 64 bf16 block (swizzled) into this rank's partial buffer (rows of 128 bytes, contiguous).
-__device__ __forceinline__ void ar_store_partial(const GemmParams& p, const uint8_t* stage, __nv_bfloat16* blk,
-                                                 long long row0, int lane) {
-  const int rg = lane >> 3, cg = lane & 7;
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int rl = it * 4 + rg;
-    if (row0 + rl >= p.M) continue;
-    *reinterpret_cast<uint4*>(blk + rl * 64 + cg * 8) =
-        *reinterpret_cast<const uint4*>(stage + rl * 128 + ((cg ^ (rl & 7)) << 4));
-  }
-}
 // Sum one 32 x 64 block over all ranks (fixed rank order), add bias / residual, write it to every rank's output.
 __device__ __forceinline__ void ar_reduce_block(const GemmParams& p, long long blk_off, long long row0, long long col0,
                                                 int lane) {

@@ -23,6 +23,16 @@
 
 namespace dptb {
 
+// Opt-in timeline (compile with -DDPTB_SKINNY_PROFILE): globaltimer stamps (ns) of work unit 0 and of the last unit of
+// tile 0: [0] kernel entry  [1] barriers + TMEM ready  [2] first stage landed  [3] accumulator complete
+// [4] partials written  [5] tile counter known  [6] splits folded  [7] output written
+#ifdef DPTB_SKINNY_PROFILE
+__device__ unsigned long long g_skinny_prof[8];
+#define SK_STAMP(slot, cond) do { if (cond) g_skinny_prof[slot] = global_timer_ns(); } while (0)
+#else
+#define SK_STAMP(slot, cond)
+#endif
+
 constexpr int kSkBM = 128;       // weight rows per CTA
 constexpr int kSkBK = 64;
 constexpr int kSkStages = 8;
@@ -49,6 +59,7 @@ struct SkinnyParams {
   const __nv_bfloat16* residual;    // [M, ldr] or null
   long long ldr;
   int num_kb, splits, kb_per_split;
+  int vec_out;                      // C / residual 16-byte aligned, leading dimensions and N multiples of 8
   float* ws;                        // [tile][split][MP][128] fp32
   int* counters;                    // per tile, zero between launches
   SkinnyAr ar;
@@ -103,6 +114,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
   const uint32_t ar_epoch = p.ar.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u : 0u;
 
+  SK_STAMP(0, blockIdx.x == 0 && threadIdx.x == 0);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *epi_ctr = 0;
@@ -127,6 +139,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  SK_STAMP(1, blockIdx.x == 0 && threadIdx.x == 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -162,6 +175,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const int s = consumed % kSkStages;
         const uint32_t ph = (consumed / kSkStages) & 1;
         if (!mbar_wait(&full_bar[s], ph, abort_flag, kWaitFullTimeout)) { ok = false; break; }
+        SK_STAMP(2, blockIdx.x == 0 && kb == kb0);
         tc_fence_after_sync();
         const uint32_t w_addr = smem_u32(smem + s * L::kStage);
         const uint32_t x_addr = w_addr + L::kWBytes;
@@ -213,6 +227,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     };
     bool ok = kb1 > kb0;
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, abort_flag, kWaitTmemFullTimeout));
+    SK_STAMP(3, blockIdx.x == 0 && et == 0);
     float v[MP];
 #pragma unroll
     for (int m = 0; m < MP; ++m) v[m] = 0.0f;
@@ -235,6 +250,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int m = 0; m < MP; ++m) mine[m * kSkBM + n_local] = v[m];
       __threadfence();
       ok = epi_sync();
+      SK_STAMP(4, blockIdx.x == 0 && et == 0);
       if (ok && et == 0) {
         const int old = atomicAdd(&p.counters[tile], 1);
         const int last = old == p.splits - 1;
@@ -243,19 +259,50 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       if (ok) ok = epi_sync();
       have_tile = ok && *epi_last != 0;
+      SK_STAMP(5, tile == 0 && have_tile && et == 0);
       if (have_tile) {
         __threadfence();
         const float* base = p.ws + (size_t)tile * p.splits * (MP * kSkBM) + n_local;
 #pragma unroll
         for (int m = 0; m < MP; ++m) v[m] = 0.0f;
-        for (int sp = 0; sp < p.splits; ++sp) {
+#pragma unroll 4
+        for (int sp = 0; sp < p.splits; ++sp) {   // several splits' loads in flight; additions stay in split order
           const float* src = base + (size_t)sp * (MP * kSkBM);
 #pragma unroll
           for (int m = 0; m < MP; ++m) v[m] += __ldcg(src + m * kSkBM);
         }
       }
     }
-    if (have_tile && p.ar.world == 0) {
+    SK_STAMP(6, tile == 0 && have_tile && et == 0);
+    if (have_tile && p.ar.world == 0 && p.vec_out) {
+      // Transpose through shared memory (the ring is idle by now) so that the output leaves as 16-byte vectors:
+      // fp32 [MP][128] staging, then 16 lanes per output row.
+      float* tile_s = reinterpret_cast<float*>(smem);
+      const float b = (p.bias && n0 + n_local < p.N) ? __bfloat162float(p.bias[n0 + n_local]) : 0.0f;
+#pragma unroll
+      for (int m = 0; m < MP; ++m) tile_s[m * kSkBM + n_local] = v[m] + b;
+      ok = epi_sync();
+      const int cg = et & 15;
+      const int col = n0 + cg * 8;
+      if (ok && col < p.N) {
+        for (int m = et >> 4; m < p.M; m += 8) {
+          const float4 lo = *reinterpret_cast<const float4*>(tile_s + m * kSkBM + cg * 8);
+          const float4 hi = *reinterpret_cast<const float4*>(tile_s + m * kSkBM + cg * 8 + 4);
+          float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          if (p.residual) {
+            const uint4 r = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + col);
+            const float2 r0 = unpack_bf16x2(r.x), r1 = unpack_bf16x2(r.y), r2 = unpack_bf16x2(r.z), r3 = unpack_bf16x2(r.w);
+            f[0] += r0.x; f[1] += r0.y; f[2] += r1.x; f[3] += r1.y;
+            f[4] += r2.x; f[5] += r2.y; f[6] += r3.x; f[7] += r3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+          o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+          *reinterpret_cast<uint4*>(p.C + (long long)m * p.ldc + col) = o;
+        }
+      }
+      SK_STAMP(7, tile == 0 && et == 0);
+    } else if (have_tile && p.ar.world == 0) {
       skinny_store<MP>(p, n0 + n_local, v);
     } else if (have_tile) {
       // Local tile -> symmetric partial buffer [tile][m][128]; flag the owner; the owner reduces and broadcasts.
@@ -357,6 +404,16 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
 
 using namespace dptb;
 
+// Timeline stamps (see DPTB_SKINNY_PROFILE); -5 when not compiled in.
+extern "C" int dptb_gemm_skinny_profile_read(unsigned long long* out) {
+#ifdef DPTB_SKINNY_PROFILE
+  return (int)cudaMemcpyFromSymbol(out, g_skinny_prof, sizeof(unsigned long long) * 8);
+#else
+  (void)out;
+  return kErrUnsupported;
+#endif
+}
+
 // out[M, N] = x[M, K] @ W[N, K]^T (+ bias) (+ residual), M <= 64, bf16 everywhere; with `ar` the sum over the ranks of a
 // tensor-parallel group lands in every rank's output (C of the argument block is then ignored).  Returns
 // kErrUnsupported for anything else, so callers can fall back to dptb_gemm / dptb_gemm_allreduce.
@@ -404,6 +461,8 @@ extern "C" int dptb_gemm_skinny(const DptbGemmArgs* a, const DptbTpArArgs* ar, v
   p.bias = static_cast<const __nv_bfloat16*>(a->bias);
   p.residual = static_cast<const __nv_bfloat16*>(a->residual); p.ldr = a->ldr;
   p.num_kb = num_kb; p.splits = splits; p.kb_per_split = kb_per_split;
+  p.vec_out = (al16(a->C) && a->ldc % 8 == 0 && a->N % 8 == 0 &&
+               (!a->residual || (al16(a->residual) && a->ldr % 8 == 0))) ? 1 : 0;
   p.ws = static_cast<float*>(a->ws);
   p.counters = a->counters;
   p.ar.world = 0;
