@@ -51,6 +51,22 @@ struct SkinnyAr {
   unsigned int* exit_counter;
 };
 
+// One-shot all-reduce for these small outputs (a few hundred KB per rank): every rank stores the fp32 tile it finished
+// into slot [parity][its rank][tile] of EVERY rank's symmetric slot buffer, each value as one 8-byte word {fp32 bits,
+// launch number} (a single-copy-atomic store, so a word that shows the launch number also shows the value); a rank
+// then polls the slots of all ranks in its OWN memory and sums them in rank order.  One NVLink hop instead of gather +
+// broadcast, no fence, no flag, no end-of-kernel handshake.  Slots alternate between two halves by launch parity: a
+// rank finishes launch e - 1 only after it has received all tiles of e - 1 from every rank, so every rank has started
+// e - 1 and hence finished reading the slots of e - 2 before anyone overwrites them in launch e.
+struct SkinnyOneShot {
+  int world, rank;
+  uint2* slots_local;                 // [2][kMaxRanks][max_tiles][64][128] words
+  uint2* slots_peer[kMaxRanks];
+  int max_tiles;
+  uint32_t* epoch;                    // local launch counter
+  unsigned int* exit_counter;         // local, zero between launches
+};
+
 struct SkinnyParams {
   int M, N, K;
   __nv_bfloat16* C;
@@ -63,7 +79,26 @@ struct SkinnyParams {
   float* ws;                        // [tile][split][MP][128] fp32
   int* counters;                    // per tile, zero between launches
   SkinnyAr ar;
+  SkinnyOneShot os;
 };
+
+// 8-byte words of the flag-in-data protocol: one single-copy-atomic access each, at system scope.
+__device__ __forceinline__ void st_relaxed_sys_v2(uint2* p, uint32_t a, uint32_t b) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_v4(uint2* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const uint2* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 
 template <int MP>
 struct SkinnySmem {
@@ -113,6 +148,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
   const uint32_t ar_epoch = p.ar.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u : 0u;
+  const uint32_t os_epoch = p.os.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.os.epoch) + 1u : 0u;
 
   SK_STAMP(0, blockIdx.x == 0 && threadIdx.x == 0);
   if (threadIdx.x == 0) {
@@ -274,7 +310,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
     SK_STAMP(6, tile == 0 && have_tile && et == 0);
-    if (have_tile && p.ar.world == 0 && p.vec_out) {
+    if (have_tile && p.ar.world == 0 && p.os.world == 0 && p.vec_out) {
       // Transpose through shared memory (the ring is idle by now) so that the output leaves as 16-byte vectors:
       // fp32 [MP][128] staging, then 16 lanes per output row.
       float* tile_s = reinterpret_cast<float*>(smem);
@@ -302,8 +338,96 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
       }
       SK_STAMP(7, tile == 0 && et == 0);
-    } else if (have_tile && p.ar.world == 0) {
+    } else if (have_tile && p.ar.world == 0 && p.os.world == 0) {
       skinny_store<MP>(p, n0 + n_local, v);
+    } else if (have_tile && p.os.world > 0) {
+      // ---- one-shot all-reduce, flag-in-data: every value travels as one 8-byte store {fp32 bits, launch number}
+      // into slot [parity][this rank][tile] of EVERY rank; a receiver polls the slots of all ranks in its own memory
+      // until every word carries this launch's number and sums them in rank order.  No fence, no separate flag.
+      const size_t tile_elems = (size_t)MP * kSkBM;
+      const size_t rank_stride = (size_t)p.os.max_tiles * 64 * kSkBM;
+      const size_t half_off = (size_t)(os_epoch & 1u) * kMaxRanks * rank_stride;
+      float* tile_s = reinterpret_cast<float*>(smem);           // the ring is idle by now
+#pragma unroll
+      for (int m = 0; m < MP; ++m) tile_s[m * kSkBM + n_local] = v[m];
+      ok = epi_sync();
+      const int cg = et & 15;
+      const int col = n0 + cg * 8;
+      const size_t in_tile = (size_t)tile * tile_elems + cg * 8;
+      if (ok) {
+        const size_t mine = half_off + (size_t)p.os.rank * rank_stride + in_tile;
+        for (int m = et >> 4; m < p.M; m += 8) {
+          const float4 lo = *reinterpret_cast<const float4*>(tile_s + m * kSkBM + cg * 8);
+          const float4 hi = *reinterpret_cast<const float4*>(tile_s + m * kSkBM + cg * 8 + 4);
+          const float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          for (int r = 0; r < p.os.world; ++r) {
+            uint2* dst = p.os.slots_peer[r] + mine + (size_t)m * kSkBM;
+            // two self-validating words per 16-byte store: halves the number of NVLink packets, and a store that the
+            // fabric split in two would still deliver two consistent words
+#pragma unroll
+            for (int e = 0; e < 8; e += 2)
+              st_relaxed_sys_v4(dst + e, __float_as_uint(f[e]), os_epoch, __float_as_uint(f[e + 1]), os_epoch);
+          }
+        }
+      }
+      SK_STAMP(5, tile == 0 && et == 0);
+      if (ok && col < p.N) {
+        float bias8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (p.bias) {
+          const uint4 braw = *reinterpret_cast<const uint4*>(p.bias + col);
+          const float2 b0 = unpack_bf16x2(braw.x), b1 = unpack_bf16x2(braw.y), b2 = unpack_bf16x2(braw.z),
+                       b3 = unpack_bf16x2(braw.w);
+          bias8[0] = b0.x; bias8[1] = b0.y; bias8[2] = b1.x; bias8[3] = b1.y;
+          bias8[4] = b2.x; bias8[5] = b2.y; bias8[6] = b3.x; bias8[7] = b3.y;
+        }
+        for (int m = et >> 4; m < p.M && ok; m += 8) {
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int r = 0; r < p.os.world && ok; ++r) {    // fixed rank order: every rank computes the same bits
+            const uint2* src = p.os.slots_local + half_off + (size_t)r * rank_stride + in_tile + (size_t)m * kSkBM;
+            uint2 w[8];
+            uint64_t t0 = 0;
+            uint32_t spins = 0;
+            while (true) {
+              bool all = true;
+#pragma unroll
+              for (int e = 0; e < 8; e += 2) {
+                const uint4 q4 = ld_relaxed_sys_v4(src + e);
+                w[e] = make_uint2(q4.x, q4.y);
+                w[e + 1] = make_uint2(q4.z, q4.w);
+                all = all && (q4.y == os_epoch) && (q4.w == os_epoch);
+              }
+              if (all) break;
+              if ((++spins & 0x3f) == 0) {
+                if (*abort_flag) { ok = false; break; }
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > kWaitLimitNs) {
+                  *abort_flag = 1;
+                  report_error(kWaitFlagTimeout);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[e] += __uint_as_float(w[e].x);
+          }
+          if (!ok) break;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += bias8[e];
+          if (p.residual) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + (long long)m * p.ldr + col);
+            const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z), r3 = unpack_bf16x2(rr.w);
+            acc[0] += r0.x; acc[1] += r0.y; acc[2] += r1.x; acc[3] += r1.y;
+            acc[4] += r2.x; acc[5] += r2.y; acc[6] += r3.x; acc[7] += r3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(p.C + (long long)m * p.ldc + col) = o;
+        }
+      }
+      SK_STAMP(7, tile == 0 && et == 0);
     } else if (have_tile) {
       // Local tile -> symmetric partial buffer [tile][m][128]; flag the owner; the owner reduces and broadcasts.
       __nv_bfloat16* ptile = p.ar.partial + (size_t)tile * (MP * kSkBM);
@@ -371,6 +495,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tc_fence_after_sync();
     tmem_dealloc<TMEM_COLS>(tmem_base);
   }
+  if (p.os.world > 0 && threadIdx.x == 0) {
+    // Launch counter of the one-shot protocol: advanced by the last CTA to leave (no cross-rank handshake).
+    __threadfence();
+    if (atomicAdd(p.os.exit_counter, 1u) == gridDim.x - 1) {
+      *p.os.exit_counter = 0;
+      *p.os.epoch = os_epoch;
+    }
+  }
   if (p.ar.world > 0 && threadIdx.x == 0) {
     // This rank's output is final once every rank has finished the tiles it owns.
     __threadfence_system();
@@ -404,6 +536,15 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
 
 using namespace dptb;
 
+// Peer-memory description of the one-shot all-reduce (see SkinnyOneShot); every rank's slot buffer holds
+// 2 * kMaxRanks * max_tiles * 64 * 128 eight-byte words, zero-initialised.
+struct DptbTpOneShotArgs {
+  int world, rank, max_tiles, reserved;
+  void* slots_peer[kDptbMaxRanks];
+  void* epoch;
+  void* exit_counter;
+};
+
 // Timeline stamps (see DPTB_SKINNY_PROFILE); -5 when not compiled in.
 extern "C" int dptb_gemm_skinny_profile_read(unsigned long long* out) {
 #ifdef DPTB_SKINNY_PROFILE
@@ -417,7 +558,17 @@ extern "C" int dptb_gemm_skinny_profile_read(unsigned long long* out) {
 // out[M, N] = x[M, K] @ W[N, K]^T (+ bias) (+ residual), M <= 64, bf16 everywhere; with `ar` the sum over the ranks of a
 // tensor-parallel group lands in every rank's output (C of the argument block is then ignored).  Returns
 // kErrUnsupported for anything else, so callers can fall back to dptb_gemm / dptb_gemm_allreduce.
+static int skinny_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTpOneShotArgs* os, void* stream_v);
 extern "C" int dptb_gemm_skinny(const DptbGemmArgs* a, const DptbTpArArgs* ar, void* stream_v) {
+  return skinny_impl(a, ar, nullptr, stream_v);
+}
+// Same product with the one-shot all-reduce: the sum over the ranks (+ bias, + residual) is written to C of the
+// argument block, which is this rank's own output buffer; every rank computes identical bits.
+extern "C" int dptb_gemm_skinny_oneshot(const DptbGemmArgs* a, const DptbTpOneShotArgs* os, void* stream_v) {
+  if (!os) return kErrBadShape;
+  return skinny_impl(a, nullptr, os, stream_v);
+}
+static int skinny_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTpOneShotArgs* os, void* stream_v) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
   if (a->M <= 0 || a->N <= 0) return 0;
   if (a->M > 64 || a->K <= 0 || a->trans_a || !a->trans_b || a->a_f32 || a->b_f32 || a->out_f32 || a->accumulate ||
@@ -429,6 +580,12 @@ extern "C" int dptb_gemm_skinny(const DptbGemmArgs* a, const DptbTpArArgs* ar, v
     if (ar->mode != 0 || ar->world < 1 || ar->world > kMaxRanks || ar->rank < 0 || ar->rank >= ar->world)
       return kErrUnsupported;
     if ((a->N % 8) || (a->ldc % 8) || (a->bias && !al16(a->bias)) ||
+        (a->residual && (!al16(a->residual) || a->ldr % 8)))
+      return kErrUnsupported;
+  }
+  if (os) {
+    if (os->world < 1 || os->world > kMaxRanks || os->rank < 0 || os->rank >= os->world) return kErrUnsupported;
+    if (!al16(a->C) || (a->N % 8) || (a->ldc % 8) || (a->bias && !al16(a->bias)) ||
         (a->residual && (!al16(a->residual) || a->ldr % 8)))
       return kErrUnsupported;
   }
@@ -466,6 +623,16 @@ extern "C" int dptb_gemm_skinny(const DptbGemmArgs* a, const DptbTpArArgs* ar, v
   p.ws = static_cast<float*>(a->ws);
   p.counters = a->counters;
   p.ar.world = 0;
+  p.os.world = 0;
+  if (os) {
+    if (tiles > os->max_tiles) return kErrTooLarge;
+    p.os.world = os->world; p.os.rank = os->rank;
+    p.os.slots_local = static_cast<uint2*>(os->slots_peer[os->rank]);
+    for (int r = 0; r < kMaxRanks; ++r) p.os.slots_peer[r] = static_cast<uint2*>(os->slots_peer[r]);
+    p.os.max_tiles = os->max_tiles;
+    p.os.epoch = static_cast<uint32_t*>(os->epoch);
+    p.os.exit_counter = static_cast<unsigned int*>(os->exit_counter);
+  }
   if (ar) {
     if (tiles > ar->max_tiles || (long long)tiles * mp * kSkBM > ar->partial_elems) return kErrTooLarge;
     p.ar.world = ar->world; p.ar.rank = ar->rank;

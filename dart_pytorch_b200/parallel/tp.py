@@ -42,6 +42,11 @@ class TpAgArgs(ctypes.Structure):
                 ("a_peer", c_void_p * MAX_RANKS), ("ready", c_void_p), ("epoch", c_void_p)]
 
 
+class TpOneShotArgs(ctypes.Structure):
+    _fields_ = [("world", c_int), ("rank", c_int), ("max_tiles", c_int), ("reserved", c_int),
+                ("slots_peer", c_void_p * MAX_RANKS), ("epoch", c_void_p), ("exit_counter", c_void_p)]
+
+
 class TpSignalArgs(ctypes.Structure):
     _fields_ = [("world", c_int), ("rank", c_int), ("ready_peer", c_void_p * MAX_RANKS), ("epoch", c_void_p)]
 
@@ -57,6 +62,8 @@ def _declare(lib):
     lib.dptb_tp_signal.restype = c_int
     lib.dptb_gemm_skinny.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpArArgs), c_void_p]
     lib.dptb_gemm_skinny.restype = c_int
+    lib.dptb_gemm_skinny_oneshot.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpOneShotArgs), c_void_p]
+    lib.dptb_gemm_skinny_oneshot.restype = c_int
 
 
 def shard_range(total: int, rank: int, world: int):
@@ -140,6 +147,25 @@ class TpComm:
         for r in range(MAX_RANKS):
             self._sig.ready_peer[r] = int(self._h_ready.buffer_ptrs[r]) if r < self.world else None
         self._sig.epoch = self.ag_epoch.data_ptr()
+        # One-shot all-reduce of decode-sized outputs (csrc/gemm_skinny.cu): per-rank tile slots on every rank, one
+        # 8-byte word {fp32 bits, launch number} per value, two halves alternating by launch parity, and the local
+        # launch counter (starts at 0, so zeroed slots never look valid).
+        self._os = None
+        if os.environ.get("DPTB200_TP_ONESHOT", "1") != "0":
+            os_tiles = (width + 127) // 128
+            self.os_slots = symm_mem.empty(2 * MAX_RANKS * os_tiles * 64 * 128, dtype=torch.int64, device=dev)
+            self.os_slots.zero_()
+            self._h_os_slots = symm_mem.rendezvous(self.os_slots, group=gname)
+            self.os_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.os_exit = torch.zeros(1, dtype=torch.int32, device=dev)
+            o = TpOneShotArgs()
+            o.world, o.rank, o.max_tiles = self.world, self.rank, os_tiles
+            for r in range(MAX_RANKS):
+                o.slots_peer[r] = int(self._h_os_slots.buffer_ptrs[r]) if r < self.world else None
+            o.epoch, o.exit_counter = self.os_epoch.data_ptr(), self.os_exit.data_ptr()
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)      # every rank's slots are zero before anyone stores into them
+            self._os = o
 
     def buffer(self, index: int, rows: int) -> torch.Tensor:
         """First ``rows`` rows of activation buffer ``index`` (this rank's copy)."""
@@ -189,7 +215,11 @@ class TpComm:
             g.splits = 0
             g.ws, g.ws_bytes = ws.data_ptr(), ws.numel()
             g.counters, g.num_counters = counters.data_ptr(), counters.numel()
-            rc = self.lib.dptb_gemm_skinny(ctypes.byref(g), ctypes.byref(args), N.stream_ptr())
+            if self._os is not None:
+                # one-shot all-reduce: every rank multicasts its tile and sums all tiles itself (one NVLink hop)
+                rc = self.lib.dptb_gemm_skinny_oneshot(ctypes.byref(g), ctypes.byref(self._os), N.stream_ptr())
+            else:
+                rc = self.lib.dptb_gemm_skinny(ctypes.byref(g), ctypes.byref(args), N.stream_ptr())
             if rc != K.ERR_UNSUPPORTED:
                 N.check(rc, "gemm_skinny_allreduce")
                 return out
