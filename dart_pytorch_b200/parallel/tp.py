@@ -150,8 +150,12 @@ class TpComm:
         # One-shot all-reduce of decode-sized outputs (csrc/gemm_skinny.cu): per-rank tile slots on every rank, one
         # 8-byte word {fp32 bits, launch number} per value, two halves alternating by launch parity, and the local
         # launch counter (starts at 0, so zeroed slots never look valid).
+        # Every rank receives (world - 1) tiles as 16-byte NVLink packets, so the scheme pays off for small groups:
+        # measured on the Llama-3-8B TP shapes, 3.70 vs 5.08 ms per decode step with 2 ranks, but 6.65 vs 5.85 ms with
+        # 8 ranks, where the gather + broadcast epilogue moves 1/8 of the bytes.  DPTB200_TP_ONESHOT=1 / 0 forces it.
         self._os = None
-        if os.environ.get("DPTB200_TP_ONESHOT", "1") != "0":
+        want_os = os.environ.get("DPTB200_TP_ONESHOT")
+        if (want_os == "1") or (want_os is None and self.world <= 4):
             os_tiles = (width + 127) // 128
             self.os_slots = symm_mem.empty(2 * MAX_RANKS * os_tiles * 64 * 128, dtype=torch.int64, device=dev)
             self.os_slots.zero_()
