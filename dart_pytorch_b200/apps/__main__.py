@@ -3,7 +3,13 @@
 transformer_lm,aft,moe}``, ``vit_demo``, ``train_muzero_lm_demo``; runners ``gpt2`` / ``distilgpt2`` / ``pythia`` /
 ``gptj`` / ``llama_chat`` with ``--serve``; ``rag_chat_server``; ``lc0_demo``; cooperative training ``coop_train_phase0``,
 ``coop_coordinator``, ``coop_worker``, ``coop_peer``; vector tools ``demo_faiss``, ``bench_faiss``, ``faiss_describe``,
-``faiss_strip``).
+``faiss_strip``; and every remaining demo / debug program — ``gpt_demo``, ``lm_demo``, ``aft_demo``, ``aft_bench``,
+``seq2seq_optim_bench``, ``word2vec_demo``, ``data_loaders_demo``, ``tutorial``, the ``vit_*`` demos,
+``train_face_folder``, ``multi_modal_demo``, ``train_multimodal_demo``, ``train_muzero_shakespeare``,
+``train_llama_vision_demo``, ``train_llava_projector``, ``llama_llava_demo``, ``llama_image_rag``, ``clip_smoke``,
+``lc0_bench_batch``, ``rag_learn``, ``rag_demo``, ``rag_gpu_demo``, ``rag_qa_demo``, ``qa``, ``vector_store_demo``,
+``gpt2_hf_demo``, the ``vector_*_demo`` programs, ``bug_repro``, ``gpt2_debug``, ``prep_coco_pairs``, ``hello`` —
+from the ``demos*.py`` modules, registered by ``all_demos()``).
 """
 from __future__ import annotations
 
@@ -319,6 +325,28 @@ def cmd_vector(args):
         open(args.csv, "w").write(vs.to_bench_csv(rows))
 
 
+DEMO_OPTIONS = {      # per-demo extra flags with their defaults (every demo also takes --device --steps --seed --model-dir)
+    "train_face_folder": {"root": ""},
+    "qa": {"corpus": None, "out": None, "question": None, "chunk_words": 120, "overlap_words": 20},
+    "gpt2_hf_demo": {"weights": None},
+    "gpt2_debug": {"weights": None},
+    "prep_coco_pairs": {"json": None, "images": None, "out": None, "n": 200},
+    "vector_index_benchmark_demo": {"n": 2000},
+    "vector_dedup_demo": {"threshold": None},
+}
+
+
+def all_demos():
+    """``{command name: function}`` for every ``demo_*`` function of the demo modules."""
+    from . import demos, demos_mm, demos_rag, demos_vector
+    out = {}
+    for mod in (demos, demos_mm, demos_rag, demos_vector):
+        for attr in sorted(dir(mod)):
+            if attr.startswith("demo_") and getattr(getattr(mod, attr), "__module__", None) == mod.__name__:
+                out[attr[len("demo_"):]] = getattr(mod, attr)
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m dart_pytorch_b200.apps")
     sub = ap.add_subparsers(dest="command", required=True)
@@ -409,6 +437,17 @@ def main(argv=None):
     p.add_argument("path")
     p.add_argument("out")
     p.set_defaults(fn=cmd_vector)
+    for name, fn in all_demos().items():
+        p = sub.add_parser(name, description=(fn.__doc__ or "").strip())
+        p.add_argument("--device", default="auto")
+        p.add_argument("--steps", type=int, default=60)
+        p.add_argument("--seed", type=int, default=0)
+        p.add_argument("--model-dir", dest="model_dir", default=None,
+                       help="downloaded Hugging Face model directory for the demos that can use pretrained weights")
+        for flag, default in DEMO_OPTIONS.get(name, {}).items():
+            kind = float if flag == "threshold" else (type(default) if default is not None else str)
+            p.add_argument("--" + flag.replace("_", "-"), dest=flag, default=default, type=kind)
+        p.set_defaults(fn=fn)
     args = ap.parse_args(argv)
     return args.fn(args)
 
