@@ -48,16 +48,18 @@ def run_ours(steps: int) -> dict:
     opt = Adam(model.parameters(), lr=LR)
     sched = LinearWarmupCosineDecay(opt, warmup_steps=WARM, total_steps=steps, max_lr=LR)
     model.train()
-    losses = []
+    losses, step_s = [], []
     t0 = time.perf_counter()
     for x, y in batches(steps):
+        t_step = time.perf_counter()
         opt.zero_grad()
         loss = model.loss(x, y)
         loss.backward()
         clip_grad_norm(model.parameters(), CLIP)
         opt.step()
         sched.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
+        step_s.append(time.perf_counter() - t_step)
     train_s = time.perf_counter() - t0
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, "tiny.dptc")
@@ -71,7 +73,7 @@ def run_ours(steps: int) -> dict:
     gen_s = time.perf_counter() - t0
     out_b = clone.generate([1.0, 2.0, 3.0], 32, temperature=0.0)
     out_nc = model.generate([1.0, 2.0, 3.0], 29, temperature=0.0, use_cache=False)
-    return {"impl": "ours", "ms_per_step": 1e3 * train_s / steps, "loss_first": losses[0], "loss_last": losses[-1],
+    return {"impl": "ours", "ms_per_step": 1e3 * train_s / steps, "median_ms_per_step": 1e3 * sorted(step_s)[len(step_s) // 2], "loss_first": losses[0], "loss_last": losses[-1],
             "checkpoint_bytes": size, "checkpoint_round_trip": bool(same),
             "generate_matches_after_reload": out_a == out_b, "cache_matches_no_cache": out_a[:len(out_nc)] == out_nc,
             "generate_ms_per_token": 1e3 * gen_s / 32, "generated": [int(t) for t in out_a]}
@@ -121,9 +123,10 @@ def run_torch(steps: int) -> dict:
         if step <= WARM:
             return LR * step / WARM
         return 0.5 * LR * (1.0 + math.cos(math.pi * (step - WARM) / (steps - WARM)))
-    losses = []
+    losses, step_s = [], []
     t0 = time.perf_counter()
     for i, (x, y) in enumerate(batches(steps)):
+        t_step = time.perf_counter()
         for g in opt.param_groups:
             g["lr"] = lr_at(i + 1)
         opt.zero_grad(set_to_none=True)
@@ -131,9 +134,10 @@ def run_torch(steps: int) -> dict:
         loss.backward()
         torch.nn.utils.clip_grad_norm_(model.parameters(), CLIP)
         opt.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
+        step_s.append(time.perf_counter() - t_step)
     train_s = time.perf_counter() - t0
-    return {"impl": "torch", "ms_per_step": 1e3 * train_s / steps, "loss_first": losses[0], "loss_last": losses[-1]}
+    return {"impl": "torch", "ms_per_step": 1e3 * train_s / steps, "median_ms_per_step": 1e3 * sorted(step_s)[len(step_s) // 2], "loss_first": losses[0], "loss_last": losses[-1]}
 
 
 def main():

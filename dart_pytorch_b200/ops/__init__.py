@@ -9,6 +9,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from . import cpu_fast as fast
 from . import reference as ref
 from .reference import causal_mask, sample_from_logits  # noqa: F401  (re-exported)
 
@@ -47,7 +48,7 @@ def linear(x, weight, bias=None, activation=None, residual=None):
         if residual is not None:
             residual = _match(residual, weight)
         return _cu().LinearFn.apply(x, weight, bias, activation, residual)
-    return ref.linear(x, weight, bias, activation, residual)
+    return fast.linear(x, weight, bias, activation, residual)
 
 
 def mlp(x, w1, b1, w2, b2, activation="relu", residual=None):
@@ -65,7 +66,7 @@ def mlp(x, w1, b1, w2, b2, activation="relu", residual=None):
 def layer_norm(x, gamma, beta=None, eps: float = 1e-5):
     if _cuda(x):
         return _cu().LayerNormFn.apply(_match(x, gamma), gamma, beta, eps, False)
-    return ref.layer_norm(x, gamma, beta, eps)
+    return fast.layer_norm(x, gamma, beta, eps)
 
 
 def rms_norm(x, gamma, eps: float = 1e-6):
@@ -79,7 +80,7 @@ def layer_norm_residual(x, gamma, beta=None, eps: float = 1e-5):
     residual branch is added inside the norm's kernel instead of by a separate add."""
     if _cuda(x):
         return _cu().LayerNormFn.apply(_match(x, gamma), gamma, beta, eps, True)
-    return x, ref.layer_norm(x, gamma, beta, eps)
+    return x, fast.layer_norm(x, gamma, beta, eps)
 
 
 def rms_norm_residual(x, gamma, eps: float = 1e-6):
@@ -92,7 +93,7 @@ def rms_norm_residual(x, gamma, eps: float = 1e-6):
 def softmax(x):
     if _cuda(x):
         return _cu().SoftmaxFn.apply(x)
-    return ref.softmax(x)
+    return fast.softmax(x)
 
 
 def cross_entropy(logits, targets):
@@ -102,7 +103,7 @@ def cross_entropy(logits, targets):
         if targets.numel() != rows:
             raise ValueError("cross_entropy: number of targets must equal number of rows")
         return _cu().CrossEntropyFn.apply(logits, ref._round_index(targets))
-    return ref.cross_entropy(logits, targets)
+    return fast.cross_entropy(logits, targets)
 
 
 def lm_head_loss(h, weight, targets):
@@ -110,7 +111,7 @@ def lm_head_loss(h, weight, targets):
     if _cuda(h):
         return _cu().LMHeadLossFn.apply(_match(h, weight), weight, ref._round_index(targets))
     logits = h @ weight.t()
-    return ref.cross_entropy(logits, targets).mean()
+    return fast.cross_entropy(logits, targets).mean()
 
 
 # --------------------------------------------------------------------------- embedding
@@ -119,7 +120,7 @@ def embedding(table, indices, pos_table=None, pos_start: int = 0):
     ``pos_start + arange(indices.shape[-1])`` are added in the same kernel."""
     if _cuda(table):
         return _cu().EmbeddingFn.apply(table, indices, pos_table, pos_start)
-    out = ref.embedding(table, indices)
+    out = fast.embedding(table, indices)
     if pos_table is not None:
         n = indices.shape[-1]
         out = out + pos_table[pos_start:pos_start + n]
@@ -138,7 +139,7 @@ def attention(q, k, v, causal: bool = False, mask=None, q_offset: int = 0):
     if _cuda(q):
         from . import flash as attn
         return attn.attention_bhsd(q, k, v, causal=causal, mask=mask, q_offset=q_offset)
-    return ref.attention(q, k, v, causal=causal, mask=mask, q_offset=q_offset)
+    return fast.attention(q, k, v, causal=causal, mask=mask, q_offset=q_offset)
 
 
 def attention_packed(qkv, batch: int, seq: int, heads: int, kv_heads: int, head_dim: int, causal: bool = True):
@@ -152,7 +153,7 @@ def attention_packed(qkv, batch: int, seq: int, heads: int, kv_heads: int, head_
     q = x[..., :d_q].reshape(batch, seq, heads, head_dim).transpose(1, 2)
     k = x[..., d_q:d_q + d_kv].reshape(batch, seq, kv_heads, head_dim).transpose(1, 2)
     v = x[..., d_q + d_kv:].reshape(batch, seq, kv_heads, head_dim).transpose(1, 2)
-    o = ref.attention(q, k, v, causal=causal)
+    o = fast.attention(q, k, v, causal=causal)
     return o.transpose(1, 2).reshape(batch * seq, d_q)
 
 
@@ -186,7 +187,7 @@ def dropout(x, p: float, training: bool, generator=None):
         return x
     if _cuda(x):
         return _cu().DropoutFn.apply(x, p)
-    return ref.dropout(x, p, training, generator)
+    return fast.dropout(x, p, training, generator)
 
 
 def swiglu(gate_up):
@@ -238,7 +239,7 @@ def sqrt(x):
 
 
 def gelu_tanh(x):
-    return _unary(x, "gelu_tanh", cpu=ref.gelu_tanh)
+    return _unary(x, "gelu_tanh", cpu=fast.gelu_tanh)
 
 
 def quick_gelu(x):

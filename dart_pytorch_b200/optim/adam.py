@@ -60,19 +60,30 @@ class Adam(Optimizer):
         self._step += 1
         bc1 = 1.0 - self.beta1 ** self._step
         bc2 = 1.0 - self.beta2 ** self._step
+        # Parameters outside an arena (CPU models, odd dtypes): the same update, m = b1 m + (1-b1) g,
+        # v = b2 v + (1-b2) g^2, p -= lr (m / bc1) / (sqrt(v / bc2) + eps) + lr wd p, as multi-tensor list ops.
         with torch.no_grad():
+            ps, gs, ms, vs = [], [], [], []
             for p in self.parameters:
                 if p.grad is None:
                     continue
-                g = p.grad
                 m = self._m.get(id(p))
-                v = self._v.get(id(p))
                 if m is None:
-                    m, v = torch.zeros_like(p), torch.zeros_like(p)
-                m = self.beta1 * m + (1.0 - self.beta1) * g
-                v = self.beta2 * v + (1.0 - self.beta2) * g * g
-                self._m[id(p)], self._v[id(p)] = m, v
-                update = self.lr * (m / bc1) / (torch.sqrt(v / bc2) + self.eps)
-                if self.weight_decay != 0.0:
-                    update = update + self.lr * self.weight_decay * p
-                p.sub_(update)
+                    m = self._m[id(p)] = torch.zeros_like(p)
+                    self._v[id(p)] = torch.zeros_like(p)
+                ps.append(p)
+                gs.append(p.grad if p.grad.dtype == p.dtype else p.grad.to(p.dtype))
+                ms.append(m)
+                vs.append(self._v[id(p)])
+            if not ps:
+                return
+            torch._foreach_mul_(ms, self.beta1)
+            torch._foreach_add_(ms, gs, alpha=1.0 - self.beta1)
+            torch._foreach_mul_(vs, self.beta2)
+            torch._foreach_addcmul_(vs, gs, gs, value=1.0 - self.beta2)
+            denom = torch._foreach_div(vs, bc2)
+            torch._foreach_sqrt_(denom)
+            torch._foreach_add_(denom, self.eps)
+            if self.weight_decay != 0.0:
+                torch._foreach_add_(ps, torch._foreach_mul(ps, -self.lr * self.weight_decay))
+            torch._foreach_addcdiv_(ps, ms, denom, value=-self.lr / bc1)

@@ -54,17 +54,16 @@ def clip_grad_norm(parameters: Sequence[torch.Tensor], max_norm: float, material
         else:
             opt.clip_pending = True
         return LazyScalar(opt.ctrl, 0)
-    total = 0.0
     grads = [p.grad for p in params if p.grad is not None]
-    for g in grads:
-        total += float((g.detach().double() ** 2).sum().item())
-    total = math.sqrt(total)
-    if total == 0.0 or not math.isfinite(total) or total <= max_norm:
-        return total
-    scale = max_norm / total
+    if not grads:
+        return 0.0
     with torch.no_grad():
-        for g in grads:
-            g.mul_(scale)
+        # per-tensor norms in one list op, combined in double precision with a single host read
+        norms = torch.stack([n.double() for n in torch._foreach_norm(grads, 2)])
+        total = float(torch.sqrt((norms * norms).sum()))
+        if total == 0.0 or not math.isfinite(total) or total <= max_norm:
+            return total
+        torch._foreach_mul_(grads, max_norm / total)
     return total
 
 

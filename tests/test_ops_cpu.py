@@ -220,3 +220,51 @@ def test_native_library_discovery_order(tmp_path, monkeypatch):
     monkeypatch.setenv("DPTB200_NATIVE_LIB", str(tmp_path / "custom.so"))
     assert N.lib_path() == tmp_path / "custom.so" and N.candidate_paths()[0] == tmp_path / "custom.so"
     assert N.build_native_library() is None          # opt-in only
+
+
+def test_fused_cpu_ops_match_the_reference_formulas_in_value_and_gradient():
+    """``ops/cpu_fast.py`` (single ATen calls, the CPU execution path) against ``ops/reference.py`` (the oracle)."""
+    from dart_pytorch_b200.ops import cpu_fast as C
+    g = torch.Generator().manual_seed(0)
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=g, dtype=torch.float64).requires_grad_()
+
+    def same(fast_fn, ref_fn, *inputs, tol=1e-9):
+        a = fast_fn(*inputs)
+        grads_a = torch.autograd.grad(a.sum() + (a * a).sum(), inputs, allow_unused=True)
+        b = ref_fn(*inputs)
+        grads_b = torch.autograd.grad(b.sum() + (b * b).sum(), inputs, allow_unused=True)
+        assert a.shape == b.shape and torch.allclose(a, b.to(a.dtype), atol=tol, rtol=tol)
+        for ga, gb in zip(grads_a, grads_b):
+            assert (ga is None) == (gb is None)
+            if ga is not None:
+                assert torch.allclose(ga, gb, atol=10 * tol, rtol=10 * tol)
+    x, w, b, r = rnd(5, 7), rnd(3, 7), rnd(1, 3), rnd(5, 3)
+    for act in (None, "relu", "gelu_tanh", "silu", "sigmoid", "tanh", "quick_gelu"):
+        same(lambda x, w, b, r: C.linear(x, w, b, act, r), lambda x, w, b, r: R.linear(x, w, b, act, r), x, w, b, r)
+    same(C.gelu_tanh, R.gelu_tanh, rnd(4, 9))
+    gam, bet = rnd(1, 7), rnd(7)
+    same(lambda x, g_, b_: C.layer_norm(x, g_, b_, 1e-5), lambda x, g_, b_: R.layer_norm(x, g_, b_, 1e-5), x, gam, bet)
+    same(lambda x, g_: C.layer_norm(x, g_, None, 1e-5), lambda x, g_: R.layer_norm(x, g_, None, 1e-5), x, gam)
+    same(C.softmax, R.softmax, rnd(2, 3, 6))
+    q, k, v = (t.detach().float().requires_grad_() for t in (rnd(2, 4, 5, 8), rnd(2, 2, 9, 8), rnd(2, 2, 9, 8)))
+    same(lambda q, k, v: C.attention(q, k, v, causal=True, q_offset=4),
+         lambda q, k, v: R.attention(q, k, v, causal=True, q_offset=4), q, k, v, tol=1e-5)   # the oracle works in fp32
+    mask = torch.randn(5, 9, generator=g)
+    same(lambda q, k, v: C.attention(q, k, v, mask=mask), lambda q, k, v: R.attention(q, k, v, mask=mask), q, k, v, tol=1e-5)
+    logits, tgt = rnd(6, 11).detach().float().requires_grad_(), torch.tensor([0, 10, 3, 3, 7, 1])
+    same(lambda l: C.cross_entropy(l, tgt), lambda l: R.cross_entropy(l, tgt), logits, tol=1e-5)
+    table = rnd(10, 4)
+    same(lambda t: C.embedding(t, torch.tensor([[1, 9], [0, 3]])), lambda t: R.embedding(t, torch.tensor([[1, 9], [0, 3]])), table)
+    oob = torch.tensor([1.0, 12.0, -3.0])
+    assert torch.equal(C.embedding(table, oob), R.embedding(table, oob)) and float(C.embedding(table, oob)[1].detach().abs().sum()) == 0
+    # other dtypes and seeded dropout keep the reference path; unseeded dropout keeps the {0, 1/(1-p)} contract
+    xb, wb = torch.randn(2, 7).bfloat16(), w.detach().bfloat16()
+    assert torch.equal(C.linear(xb, wb, None, "gelu_tanh"), R.linear(xb, wb, None, "gelu_tanh"))
+    y = C.dropout(torch.ones(2000), 0.25, True)
+    kept = y[y != 0]
+    assert torch.allclose(kept, torch.full_like(kept, 1.0 / 0.75)) and 300 < int((y == 0).sum()) < 700
+    y1 = C.dropout(torch.ones(50), 0.5, True, torch.Generator().manual_seed(3))
+    y2 = R.dropout(torch.ones(50), 0.5, True, torch.Generator().manual_seed(3))
+    assert torch.equal(y1, y2)
