@@ -155,6 +155,8 @@ class Tensor:
         s = src.t if isinstance(src, Tensor) else src
         if list(s.shape) != list(self.t.shape):
             raise ValueError(f"assign: shape mismatch {list(s.shape)} vs {list(self.t.shape)}")
+        if s.device.type != self.t.device.type:
+            raise ValueError(f"assign: device mismatch {s.device.type} vs {self.t.device.type}")
         with torch.no_grad():
             self.t.copy_(s.to(self.t.device, self.t.dtype))
 
