@@ -1,4 +1,5 @@
-"""Functional tensor ops.  CPU tensors take the pure-PyTorch reference formulas (``ops/reference.py``); CUDA tensors
+"""Functional tensor ops.  CPU tensors take the pure-PyTorch reference formulas (``ops/reference.py``, the hot ones
+through their single-call restatements in ``ops/cpu_fast.py``); CUDA tensors
 take the native sm_100a kernels through the autograd functions of ``ops/cuda.py``.  There is one code path per
 device: a CUDA tensor never falls back to a library kernel, and a missing native library raises.
 """
@@ -27,6 +28,14 @@ def _match(x: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
     return x if x.dtype == like.dtype else x.to(like.dtype)
 
 
+def _decode_half(w, like: torch.Tensor):
+    """CPU half-precision *storage* operands (weights kept as fp16 to halve memory) are widened where they are used
+    (reference: fp16 right-hand sides are decoded on the fly, lib/core/tensor/mat_mul.dart:51-76)."""
+    if w is not None and w.dtype == torch.float16 and like.dtype != torch.float16 and not w.is_cuda:
+        return w.to(like.dtype)
+    return w
+
+
 # --------------------------------------------------------------------------- matmul / linear
 def matmul(a, b):
     if b.dim() != 2:
@@ -37,7 +46,7 @@ def matmul(a, b):
         raise ValueError("matmul: operands live on different devices")
     if _cuda(a, b):
         return _cu().MatmulFn.apply(a, _match(b, a))
-    return ref.matmul(a, b)
+    return ref.matmul(a, _decode_half(b, a))
 
 
 def linear(x, weight, bias=None, activation=None, residual=None):
@@ -48,7 +57,7 @@ def linear(x, weight, bias=None, activation=None, residual=None):
         if residual is not None:
             residual = _match(residual, weight)
         return _cu().LinearFn.apply(x, weight, bias, activation, residual)
-    return fast.linear(x, weight, bias, activation, residual)
+    return fast.linear(x, _decode_half(weight, x), _decode_half(bias, x), activation, residual)
 
 
 def mlp(x, w1, b1, w2, b2, activation="relu", residual=None):

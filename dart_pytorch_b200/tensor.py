@@ -150,15 +150,28 @@ class Tensor:
 
     def assign(self, src: "Tensor") -> None:
         """Overwrite the values in place, keeping this tensor's identity (optimizer state stays attached)."""
-        if self.t.dtype == torch.float16:
-            raise RuntimeError("assign: half storage tensors are read-only")
         s = src.t if isinstance(src, Tensor) else src
+        if self.t.dtype == torch.float16 or s.dtype == torch.float16:
+            raise RuntimeError("assign: half storage tensors are read-only; promote with toFp32() first")
         if list(s.shape) != list(self.t.shape):
             raise ValueError(f"assign: shape mismatch {list(s.shape)} vs {list(self.t.shape)}")
         if s.device.type != self.t.device.type:
             raise ValueError(f"assign: device mismatch {s.device.type} vs {self.t.device.type}")
         with torch.no_grad():
             self.t.copy_(s.to(self.t.device, self.t.dtype))
+
+    def adoptCpuStorageFrom(self, source: "Tensor") -> None:
+        """Take over ``source``'s CPU buffer, dtype included (how loaders swap half-precision weights into a model
+        without a copy); this tensor keeps its shape, loses its autograd state, and ``source`` is left empty
+        (reference: lib/core/tensor/tensor.dart:442-470)."""
+        if self.t.is_cuda or source.t.is_cuda:
+            raise RuntimeError("adoptCpuStorageFrom: both tensors must be on the CPU")
+        if source.length != self.length:
+            raise ValueError(f"adoptCpuStorageFrom: length mismatch, got {source.length}, expected {self.length}")
+        self.t = source.t.detach().reshape(self.t.shape)
+        source.t = torch.empty(0)
+
+    adopt_cpu_storage_from = adoptCpuStorageFrom
 
     def sliceRows(self, start: int, end: int) -> "Tensor":
         if not (0 <= start <= end <= self.t.shape[0]):
