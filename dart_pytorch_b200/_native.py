@@ -86,6 +86,22 @@ def lib_path() -> Path:
     return build_native_library() or _HERE / "_C" / LIB_NAME
 
 
+def ensure_native_lib() -> str:
+    """Path of the native library, building it in-tree when no candidate exists (there is nothing to download: the
+    library ships as source).  An environment override that points at a missing file is an error
+    (reference contract: lib/core/tensor/native_lib_download.dart:35-48)."""
+    env = os.environ.get("DPTB200_NATIVE_LIB")
+    if env and not Path(env).exists():
+        raise NativeLibraryError(f"DPTB200_NATIVE_LIB={env} does not exist")
+    path = lib_path()
+    if not path.exists():
+        raise NativeLibraryError(f"no native library at {path}; build it with `python csrc/build.py`")
+    return str(path)
+
+
+ensureNativeLib = ensure_native_lib
+
+
 def load(required: bool = True) -> Optional[ctypes.CDLL]:
     global _LIB, _LIB_ERROR
     if _LIB is not None:

@@ -301,12 +301,31 @@ def cmd_vector(args):
     import numpy as np
     from .. import vector_store as vs
     if args.command == "faiss_describe":
-        print(vs.faiss_describe(open(args.path, "rb").read()))
-        return
+        # header-only probe (37 bytes of a plain file) as the reference tool does; --deep decodes and walks the index
+        info = vs.probe_faiss_index_file(args.path)
+        rec = {"path": args.path, "fourcc": info.fourcc_str, "kind": info.kind.value, "d": info.d,
+               "ntotal": info.ntotal, "metric": None if info.metric is None else info.metric.name,
+               "isTrained": info.is_trained, "codeSize": info.code_size}
+        if info.tuning is not None:
+            t = info.tuning
+            rec["inner"] = info.inner.fourcc_str
+            rec["tuning"] = {"createdAt": t.created_at.isoformat(), "metric": t.metric.name,
+                             "chosen": t.chosen_param_value,
+                             "points": [{"value": p.param_value, "label": p.param_label, "recall": p.recall,
+                                         "meanUs": p.mean_us} for p in t.points]}
+        print(json.dumps(rec) if args.json else "\n".join(f"{k}: {v}" for k, v in rec.items()))
+        if args.deep:
+            data = open(args.path, "rb").read()
+            print(vs.faiss_describe(vs.strip_tuning_wrapper(data) if vs.is_tuned_faiss_blob(data) else data))
+        return rec
     if args.command == "faiss_strip":
-        open(args.out, "wb").write(vs.faiss_strip(open(args.path, "rb").read()))
-        print(f"wrote {args.out}")
-        return
+        data = open(args.path, "rb").read()
+        out = args.out or (args.path[:-6] if args.path.endswith(".faiss") else args.path) + ".stripped.faiss"
+        # default: remove the tuning-metadata wrapper so that upstream FAISS can read the file;
+        # --vectors instead empties the stored vectors while keeping trained state
+        open(out, "wb").write(vs.faiss_strip(data) if args.vectors else vs.strip_tuning_wrapper(data))
+        print(f"wrote {out}")
+        return out
     rng = np.random.default_rng(0)
     cent = rng.standard_normal((32, args.d)).astype(np.float32) * 3
     x = (cent[rng.integers(32, size=args.n)] + rng.standard_normal((args.n, args.d))).astype(np.float32)
@@ -432,10 +451,13 @@ def main(argv=None):
         p.set_defaults(fn=cmd_vector)
     p = sub.add_parser("faiss_describe")
     p.add_argument("path")
+    p.add_argument("--json", action="store_true")
+    p.add_argument("--deep", action="store_true")
     p.set_defaults(fn=cmd_vector)
     p = sub.add_parser("faiss_strip")
     p.add_argument("path")
-    p.add_argument("out")
+    p.add_argument("out", nargs="?", default=None)
+    p.add_argument("--vectors", action="store_true")
     p.set_defaults(fn=cmd_vector)
     for name, fn in all_demos().items():
         p = sub.add_parser(name, description=(fn.__doc__ or "").strip())

@@ -81,6 +81,14 @@ class LmSample:
     target: torch.Tensor   # [blockSize] the same window shifted by one
 
 
+class TextEncoder:
+    """What ``TextTokenDataset.from_text`` needs of a tokenizer: ``encode(str) -> list[int]``; every tokenizer of the
+    package satisfies it (reference: lib/core/data/text_token_dataset.dart:27-29)."""
+
+    def encode(self, text: str) -> List[int]:
+        raise NotImplementedError
+
+
 class TextTokenDataset(Dataset[LmSample]):
     """Sliding next-token windows over a token stream; ``len = numTokens - blockSize``."""
 

@@ -315,3 +315,15 @@ class WordPieceTokenizer:
             else:
                 words.append(tok)
         return " ".join(words)
+
+
+def debug_preview(ids: Sequence[int], max_items: int) -> str:
+    """JSON list of the first ``max_items`` ids, with the total appended when the list is longer
+    (reference: lib/core/data/wordpiece_tokenizer.dart:315-318)."""
+    ids = [int(i) for i in ids]
+    if len(ids) <= max_items:
+        return json.dumps(ids, separators=(",", ":"))
+    return f"{json.dumps(ids[:max_items], separators=(',', ':'))} ...({len(ids)} total)"
+
+
+debugPreview = debug_preview

@@ -39,3 +39,14 @@ def fp32ListToFp16Bits(values: Iterable[float]) -> List[int]:
 def fp16BitsListToFp32(bits: Iterable[int]) -> List[float]:
     arr = [(b & 0xFFFF) - (0x10000 if (b & 0xFFFF) >= 0x8000 else 0) for b in bits]
     return fp16_bits_to_fp32(torch.tensor(arr, dtype=torch.int16)).tolist()
+
+
+def decodeFp16Bulk(bits) -> torch.Tensor:
+    """Half bit patterns (tensor, array or list of ints) -> fp32 tensor, the bulk form of ``fp16BitsToFp32``
+    (reference: lib/core/tensor/dtype.dart:122-170)."""
+    if not isinstance(bits, torch.Tensor):
+        bits = torch.as_tensor(list(bits), dtype=torch.int32)
+    return fp16_bits_to_fp32((bits.to(torch.int32) & 0xFFFF).to(torch.int16))
+
+
+decode_fp16_bulk = decodeFp16Bulk

@@ -54,6 +54,8 @@ class ShardIndex:
                 out.append(v)
         return out
 
+    shardFiles = shard_files = shards
+
 
 def _data_offset(buf) -> int:
     if len(buf) < 8:

@@ -77,6 +77,7 @@ class MHACache:
         self.k_buf[:, self.seq_len:self.seq_len + s] = k_new
         self.v_buf[:, self.seq_len:self.seq_len + s] = v_new
         self.seq_len += s
+        self.__dict__.pop("_fills", None)
         return self.k_buf[:, :self.seq_len], self.v_buf[:, :self.seq_len]
 
     # Per-head accessors with the reference's shapes (``[T_seen, hd]``, batch 1).
@@ -92,8 +93,33 @@ class MHACache:
     def v(self) -> List[Optional[torch.Tensor]]:
         return [None if self.v_buf is None else self._head(self.v_buf, h) for h in range(self.num_kv_heads)]
 
+    # Per-head appends with the reference's signature (``[N_new, hd]`` for one KV head; returns that head's full
+    # history).  They write into the same buffers; the cache length follows the furthest head.
+    def _append_head(self, which: str, kv_head: int, new: torch.Tensor) -> torch.Tensor:
+        if not (0 <= kv_head < self.num_kv_heads):
+            raise IndexError(f"MHACache: kv head {kv_head} out of range [0, {self.num_kv_heads})")
+        n, hd = new.shape
+        fills = self.__dict__.setdefault("_fills", {"base": self.seq_len})    # rows valid before per-head appends began
+        fill = fills.setdefault(which, [fills["base"]] * self.num_kv_heads)
+        start = fill[kv_head]
+        self._ensure(1, start + n, self.num_kv_heads * hd, new)
+        buf = self.k_buf if which == "k" else self.v_buf
+        buf[0, start:start + n, kv_head * hd:(kv_head + 1) * hd] = new.detach()
+        fill[kv_head] = start + n
+        self.seq_len = max(self.seq_len, start + n)
+        return buf[0, :start + n, kv_head * hd:(kv_head + 1) * hd]
+
+    def append_k(self, kv_head: int, new_k: torch.Tensor) -> torch.Tensor:
+        return self._append_head("k", kv_head, new_k)
+
+    def append_v(self, kv_head: int, new_v: torch.Tensor) -> torch.Tensor:
+        return self._append_head("v", kv_head, new_v)
+
+    appendK, appendV = append_k, append_v
+
     def reset(self) -> None:
         self.seq_len = 0
+        self.__dict__.pop("_fills", None)
 
 
 class EncoderCache:

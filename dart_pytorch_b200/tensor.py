@@ -29,6 +29,13 @@ class DType(str, Enum):
     fp16 = "fp16"
     bf16 = "bf16"
 
+    @property
+    def itemBytes(self) -> int:
+        """Bytes per stored element (reference: lib/core/tensor/dtype.dart:41-44)."""
+        return 4 if self is DType.fp32 else 2
+
+    item_bytes = itemBytes
+
 
 AUTO_DEVICE_THRESHOLD = 4096  # reference: tensors of at least this many elements default to the GPU when one exists
 
@@ -114,6 +121,24 @@ class Tensor:
     @property
     def grad(self) -> Optional["Tensor"]:
         return None if self.t.grad is None else Tensor(self.t.grad)
+
+    @property
+    def debugChildShapes(self) -> List[List[int]]:
+        """Shapes of this tensor's autograd children, for debugging a graph (reference: tensor.dart:74-76).  Leaf
+        children report their own shape; interior children the shape their producer recorded, when it recorded one."""
+        fn = self.t.grad_fn
+        out: List[List[int]] = []
+        for nxt, idx in (fn.next_functions if fn is not None else ()):
+            if nxt is None:
+                continue
+            var = getattr(nxt, "variable", None)
+            if var is not None:
+                out.append(list(var.shape))
+                continue
+            meta = getattr(nxt, "_input_metadata", None)
+            if meta is not None and idx < len(meta):
+                out.append([int(s) for s in meta[idx].shape])
+        return out
 
     @property
     def residentBytes(self) -> int:

@@ -654,3 +654,10 @@ def faiss_strip(data: bytes) -> bytes:
 
 writeFaissIndex, readFaissIndex = write_faiss_index, read_faiss_index
 writeFaissBinaryIndex, readFaissBinaryIndex = write_faiss_binary_index, read_faiss_binary_index
+# the reference's names for the file / byte entry points
+saveFaissIndex, loadFaissIndex = write_faiss_index, read_faiss_index
+saveFaissBinaryIndex, loadFaissBinaryIndex = write_faiss_binary_index, read_faiss_binary_index
+writeFaissIndexToBytes, readFaissIndexFromBytes = write_faiss_index_bytes, read_faiss_index_bytes
+writeFaissBinaryIndexToBytes, readFaissBinaryIndexFromBytes = (write_faiss_binary_index_bytes,
+                                                               read_faiss_binary_index_bytes)
+FaissFourcc.toStr = FaissFourcc.name

@@ -14,7 +14,7 @@ from typing import List, Optional, Set
 
 import numpy as np
 
-from .base import Index, Metric, SearchResult, as_rows, pairwise_scores, select_topk
+from .base import Index, Metric, RangeSearchResult, SearchResult, as_rows, pairwise_scores, select_topk
 from .flat import IndexFlat, Kmeans, _RowStore
 
 
@@ -188,6 +188,26 @@ class IndexIVFFlat(_IVFBase):
             out_i.append(ii[0])
         return SearchResult(np.stack(out_d) if out_d else np.zeros((0, k), np.float32),
                             np.stack(out_i) if out_i else np.zeros((0, k), np.int64))
+
+    def range_search(self, queries, radius: float) -> RangeSearchResult:
+        """Every stored vector of the ``nprobe`` probed cells within ``radius`` (L2: distance below it, inner product:
+        similarity above it), best first; equals the flat result when ``nprobe == nlist``
+        (reference: lib/core/vector_store/index_ivf_flat.dart:173-215)."""
+        if not self.is_trained:
+            raise RuntimeError("IndexIVFFlat.rangeSearch before train()")
+        q = as_rows(queries, self.d)
+        probes = self._probe(q)
+        dist_rows, id_rows = [], []
+        for qi in range(len(q)):
+            ids = np.fromiter((i for c in probes[qi] if c >= 0 for i in self._inv_lists[int(c)]), dtype=np.int64)
+            scores = pairwise_scores(q[qi:qi + 1], self._store.view[ids], self.metric) if len(ids) else \
+                np.zeros((1, 0), np.float32)
+            one = self._range_from_scores(scores, radius, ids)
+            dist_rows.append(one.distances)
+            id_rows.append(one.ids)
+        return RangeSearchResult.from_per_query(dist_rows, id_rows)
+
+    rangeSearch = range_search
 
     def remove_ids(self, ids: Set[int]) -> int:
         hit = sorted(i for i in ids if 0 <= i < self.ntotal)

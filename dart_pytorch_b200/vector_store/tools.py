@@ -406,4 +406,14 @@ def auto_tune_m(source_vectors, queries, k: int, truth: SearchResult, values: Se
     return TuneMResult(points, built, chosen, built.get(chosen.param_value) if chosen else None)
 
 
+def auto_tune_m_from_flat(source: IndexFlat, queries, k: int, truth: SearchResult, values: Sequence[int] = (4, 8, 16),
+                          **kw) -> TuneMResult:
+    """``auto_tune_m`` over the vectors (and metric) already held by a flat index
+    (reference: lib/core/vector_store/auto_tune.dart:343-378)."""
+    if source.ntotal == 0:
+        raise ValueError("autoTuneMFromFlat: source index is empty")
+    return auto_tune_m(reconstruct_all(source), queries, k, truth, values=values, metric=source.metric, **kw)
+
+
 autoTuneNprobe, autoTuneEfSearch, autoTuneM = auto_tune_nprobe, auto_tune_ef_search, auto_tune_m
+autoTuneMFromFlat = auto_tune_m_from_flat

@@ -204,3 +204,19 @@ def test_gpt_batched_forward_and_training_step():
         last = float(loss.detach())
         first = last if first is None else first
     assert last < 0.7 * first
+
+
+def test_per_head_cache_appends_with_the_reference_signature():
+    c = MHACache(2)
+    k0 = c.appendK(0, torch.ones(3, 4))
+    c.appendK(1, 2 * torch.ones(3, 4))
+    c.appendV(0, 5 * torch.ones(3, 4))
+    c.appendV(1, 6 * torch.ones(3, 4))
+    assert k0.shape == (3, 4) and c.seqLen == 3 and c.v[1][:, 0].tolist() == [6.0, 6.0, 6.0]
+    k1 = c.appendK(0, 3 * torch.ones(1, 4))
+    assert k1.shape == (4, 4) and k1[:, 0].tolist() == [1.0, 1.0, 1.0, 3.0] and c.seqLen == 4
+    assert c.k[1][:3, 0].tolist() == [2.0, 2.0, 2.0]
+    with pytest.raises(IndexError):
+        c.appendK(2, torch.ones(1, 4))
+    c.reset()
+    assert c.seqLen == 0 and c.appendV(1, torch.ones(2, 4)).shape == (2, 4) and c.seqLen == 2

@@ -228,3 +228,20 @@ def test_safetensors_sharded_loading(tmp_path):
     seen = []
     SafeTensors.stream_sharded(str(ipath), lambda part: seen.append(sorted(part)))
     assert seen == [["layer.0.w"], ["layer.1.w"]]
+
+
+def test_small_api_parity_items(tmp_path, monkeypatch):
+    from dart_pytorch_b200 import _native
+    from dart_pytorch_b200.data import TextEncoder, debugPreview
+    from dart_pytorch_b200.io import BertLoadReport, ClipLoadReport, GPT2LoadReport, LoadReport
+    assert dp.DType.fp16.itemBytes == 2 and dp.DType.fp32.itemBytes == 4
+    assert D.decodeFp16Bulk([0x3C00, 0xC000, 0x7BFF]).tolist() == [1.0, -2.0, 65504.0]
+    a = T.fromList([2, 3], [1, 2, 3, 4, 5, 6], requiresGrad=True)
+    b = T.fromList([3, 2], [1, 0, 0, 1, 1, 1], requiresGrad=True)
+    assert a.matmul(b).debugChildShapes == [[2, 3], [3, 2]] and a.debugChildShapes == []
+    assert debugPreview(range(10), 3) == "[0,1,2] ...(10 total)" and debugPreview([1, 2], 3) == "[1,2]"
+    assert GPT2LoadReport is LoadReport and BertLoadReport is ClipLoadReport
+    assert hasattr(TextEncoder, "encode")
+    monkeypatch.setenv("DPTB200_NATIVE_LIB", str(tmp_path / "missing.so"))
+    with pytest.raises(_native.NativeLibraryError):
+        _native.ensureNativeLib()
