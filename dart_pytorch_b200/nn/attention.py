@@ -342,6 +342,11 @@ class MultiHeadCrossAttention(Module):
     def forward(self, xq, xkv, residual=None):
         if xq.dim() != xkv.dim() or xq.dim() not in (2, 3):
             raise ValueError("MultiHeadCrossAttention: xq and xkv must both be 2-D or both 3-D")
+        if xq.shape[-1] != self.embed_dim or xkv.shape[-1] != self.kv_dim:
+            raise ValueError(f"MultiHeadCrossAttention: expected last dims {self.embed_dim} / {self.kv_dim}, got "
+                             f"{xq.shape[-1]} / {xkv.shape[-1]}")
+        if xq.dim() == 3 and xq.shape[0] != xkv.shape[0]:
+            raise ValueError(f"MultiHeadCrossAttention: batch sizes differ ({xq.shape[0]} vs {xkv.shape[0]})")
         batched = xq.dim() == 3
         B = xq.shape[0] if batched else 1
         Sq, Sk = xq.shape[-2], xkv.shape[-2]
