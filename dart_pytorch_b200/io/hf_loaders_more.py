@@ -329,9 +329,13 @@ class ClipHFLoader(_FileEntry):
 
     @classmethod
     def load_map(cls, model: CLIPVisionModel, state_in: Dict[str, torch.Tensor]) -> LoadReport:
-        prefix = "vision_model."
-        if not any(k.startswith(prefix) for k in state_in):
-            raise ValueError('clip loader: no "vision_model." tensors in the checkpoint')
+        # full CLIPModel bundles prefix every vision tensor with "vision_model."; standalone vision checkpoints and
+        # some re-exports carry bare names (reference: lib/core/nn/clip_hf_loader.dart:343-355)
+        candidates = ("vision_model.", "")
+        prefix = next((p for p in candidates if p + "embeddings.patch_embedding.weight" in state_in), None)
+        if prefix is None:
+            raise ValueError('clip loader: cannot find "embeddings.patch_embedding.weight" in the state dict (checked '
+                             f'prefixes {list(candidates)}); is this a CLIP vision checkpoint?')
         t = _Taker(state_in, "clip")
         c = model.config
         d, f, P, C = c.embed_dim, c.ffn_dim, c.patch_size, c.num_channels
