@@ -234,7 +234,7 @@ def run_torch(args):
 
 def run_reference(args):
     from baseline.reference_arm import run
-    run(args, METRIC, MODEL, SEQ)
+    run(args, METRIC, MODEL, SEQ, ClockSampler)
 
 
 if __name__ == "__main__":

@@ -2,6 +2,8 @@
 // in a fixed device array of this file instead of a caller-provided buffer.  See colsum_static.h for the contract.
 #include "colsum_static.h"
 
+#include <atomic>
+
 #include "common/host.h"
 #include "common/reduce.cuh"
 
@@ -54,18 +56,20 @@ colsum_static_final_kernel(const float* __restrict__ partial, int nparts, int co
 
 // Device address of g_colsum_scratch on the current device, resolved once per device.
 int scratch_for_current_device(float** out) {
-  static float* cached[64] = {nullptr};
+  // Host threads may make their first calls at the same time: the slots are atomics, and two threads that both find a
+  // slot empty both resolve the same address and store the same value.
+  static std::atomic<float*> cached[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return dptb::kErrBadShape;
-  if (cached[dev] == nullptr) {
-    float* p = nullptr;
+  float* p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_colsum_scratch);
     if (e != cudaSuccess) return (int)e;
-    cached[dev] = p;
+    cached[dev].store(p, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = p;
   return 0;
 }
 
@@ -89,8 +93,8 @@ extern "C" int dptb_colsum_static(const void* x, long long ld, void* out, long l
   if (dtype) colsum_static_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, rows, cols, scratch);
   else       colsum_static_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)x, ld, rows, cols, scratch);
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
+  if (e != cudaSuccess) return dptb::counted(0, (int)e);
   if (dtype) colsum_static_final_kernel<__nv_bfloat16><<<(cols + 255) / 256, 256, 0, st>>>(scratch, nparts, cols, (__nv_bfloat16*)out, accumulate);
   else       colsum_static_final_kernel<float><<<(cols + 255) / 256, 256, 0, st>>>(scratch, nparts, cols, (float*)out, accumulate);
-  return (int)cudaGetLastError();
+  return dptb::counted(2, (int)cudaGetLastError());
 }

@@ -18,15 +18,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Bounded wait for *p >= target.  Returns false (and records the failure) when it gives up.
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
+// Bounded wait for *p >= target.  Returns false (and records the failure) when it gives up after `limit_ns`.
+// The default limit suits waits inside a pipeline of kernels that run together; a wait for another rank to *reach*
+// a point of its step (which may be late by as long as its host was busy) passes its own, longer limit.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, uint64_t limit_ns = kWaitLimitNs) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while ((int32_t)(ld_acquire_sys(p) - target) < 0) {
     if ((++spins & 0x3f) == 0) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > limit_ns) {
         report_error(kWaitFlagTimeout);
         return false;
       }

@@ -18,7 +18,9 @@
 //   last CTA of the grid: fold the per-CTA sums in CTA order, publish sumsq[b][rank] and done[b][rank] = e to every peer
 // dp_finalize waits (bounded) for done[*][*] >= e, adds sumsq[*][*] in fixed order and writes the clip control block
 // {norm, scale, finite, sumsq}; the optimizer kernel that follows therefore sees fully reduced gradients.
-// Every wait is bounded; a wait that runs out records kWaitFlagTimeout in the status word and the kernel returns.
+// Every wait is bounded (`wait_ns`, a launch argument: it is the largest skew between ranks a step tolerates).  A
+// wait that runs out records kWaitFlagTimeout in the status word, and the rank publishes NaN as its sum of squares, so
+// every rank's control block reads "not finite" and an optimizer told to skip such steps leaves the weights alone.
 #include <cuda_bf16.h>
 
 #include "common/host.h"
@@ -40,6 +42,7 @@ struct DpArgs {
   float* cta_partial;                // local scratch [gridDim.x]
   unsigned int* cta_counter;         // local, zero between launches
   unsigned int* epochs;              // local [num_buckets]
+  unsigned long long wait_ns;        // limit of the wait for the peers' gradients
 };
 
 // Signal buffer layout (32-bit words): ready[b][r] | done[b][r] | sumsq[b][r] (float bits)
@@ -62,7 +65,7 @@ dp_allreduce_kernel(const DpArgs a) {
     // Tell every rank that this rank's gradients of bucket b are final (redundant across CTAs: same value).
     __threadfence_system();
     st_release_sys(a.pads[threadIdx.x] + pad_ready(nb, b, a.rank), e);
-    if (!wait_flag_ge(my_pad + pad_ready(nb, b, threadIdx.x), e)) s_ok = 0;
+    if (!wait_flag_ge(my_pad + pad_ready(nb, b, threadIdx.x), e, a.wait_ns)) s_ok = 0;
   }
   __syncthreads();
   float sq = 0.0f;
@@ -106,6 +109,7 @@ dp_allreduce_kernel(const DpArgs a) {
     }
   }
   __threadfence_system();  // this thread's slice writes are visible system-wide before the CTA reports
+  if (!s_ok && threadIdx.x == 0) sq = NAN;  // the owned slice was not averaged: poison the norm instead of hiding it
   sq = block_sum(sq, scratch);
   if (threadIdx.x == 0) {
     a.cta_partial[blockIdx.x] = sq;
@@ -135,14 +139,14 @@ dp_allreduce_kernel(const DpArgs a) {
 // One CTA: wait for every (bucket, rank) of this step, fold the sums of squares, write the clip control block.
 __global__ void __launch_bounds__(256)
 dp_finalize_kernel(const uint32_t* pad, const unsigned int* epochs, int num_buckets, int world, float max_norm,
-                   float* ctrl) {
+                   float* ctrl, unsigned long long wait_ns) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   const int total = num_buckets * world;
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int b = i / world, r = i % world;
-    if (!wait_flag_ge(pad + pad_done(num_buckets, b, r), epochs[b])) s_ok = 0;
+    if (!wait_flag_ge(pad + pad_done(num_buckets, b, r), epochs[b], wait_ns)) s_ok = 0;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -176,6 +180,7 @@ struct DptbDpArgs {
   unsigned int* epochs;
   int grid;
   int use_nvls;
+  long long wait_ns;   // <= 0: the default limit of a wait
 };
 
 // Words a signal buffer needs for `num_buckets` buckets.
@@ -195,14 +200,16 @@ extern "C" int dptb_dp_allreduce(const DptbDpArgs* h, void* stream) {
   a.rank = h->rank; a.world = h->world; a.bucket = h->bucket; a.num_buckets = h->num_buckets;
   a.start = h->start; a.n = h->n;
   a.cta_partial = h->cta_partial; a.cta_counter = h->cta_counter; a.epochs = h->epochs;
+  a.wait_ns = h->wait_ns > 0 ? (unsigned long long)h->wait_ns : kWaitLimitNs;
   if (h->use_nvls && a.mc_base) dp_allreduce_kernel<true><<<h->grid, kDpThreads, 0, st>>>(a);
   else                          dp_allreduce_kernel<false><<<h->grid, kDpThreads, 0, st>>>(a);
   return counted(1, (int)cudaGetLastError());
 }
 
 extern "C" int dptb_dp_finalize(const void* pad, const unsigned int* epochs, int num_buckets, int world,
-                                float max_norm, float* ctrl, void* stream) {
-  dp_finalize_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(pad), epochs,
-                                                                     num_buckets, world, max_norm, ctrl);
+                                float max_norm, float* ctrl, long long wait_ns, void* stream) {
+  dp_finalize_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(pad), epochs, num_buckets, world, max_norm, ctrl,
+      wait_ns > 0 ? (unsigned long long)wait_ns : kWaitLimitNs);
   return counted(1, (int)cudaGetLastError());
 }

@@ -46,8 +46,9 @@ def _moment_views(opt):
         if arena.master is not None:
             out.append(("master", per_param(arena.master)))
     else:
+        # SGD without an arena keeps its momentum per parameter in `_velocity`
         for name, store in (("m", getattr(opt, "_m", None)), ("v", getattr(opt, "_v", None)),
-                            ("buf", getattr(opt, "_buf", None))):
+                            ("buf", getattr(opt, "_velocity", None))):
             if isinstance(store, dict) and store:
                 out.append((name, [store.get(id(p)) for p in params]))
     return out
@@ -68,7 +69,7 @@ def save_train_state(path: str, optimizer=None, scheduler=None, extra: Optional[
         blobs.append(raw)
         offset += len(raw)
     if optimizer is not None:
-        o = {"kind": type(optimizer).__name__, "lr": float(optimizer.lr), "step": int(getattr(optimizer, "_step", 0)),
+        o = {"kind": type(optimizer).__name__, "lr": float(optimizer.lr), "step": int(getattr(optimizer, "_step", getattr(optimizer, "_steps", 0))),
              "num_params": len(optimizer.parameters)}
         for k in ("beta1", "beta2", "eps", "weight_decay", "momentum"):
             if hasattr(optimizer, k):
@@ -149,14 +150,20 @@ def load_train_state(path: str, optimizer=None, scheduler=None, restore_rng: boo
                     if name in targets and targets[name][i] is not None:
                         targets[name][i].copy_(src.to(targets[name][i].device))
                     elif arena is None and name != "master":
-                        store = getattr(optimizer, f"_{name}", None)
+                        store = getattr(optimizer, "_velocity" if name == "buf" else f"_{name}", None)
                         if isinstance(store, dict):
                             store[id(p)] = src.to(device=p.device, dtype=p.dtype if name == "buf" else torch.float32
                                                   if p.dtype == torch.float32 else p.dtype).clone()
             if arena is not None and arena.master is not None and any(k.startswith("opt.master.") for k in tensors):
                 arena.sync_to_params()
         optimizer.lr = float(o["lr"])
-        optimizer._step = int(o["step"])
+        if hasattr(optimizer, "_steps"):
+            # SGD: its first step *overwrites* the momentum buffer with the gradient, so a restored buffer must not be
+            # taken for a first step
+            loaded_buf = any(k.startswith("opt.buf.") for k in tensors)
+            optimizer._steps = max(int(o["step"]), 1 if loaded_buf else 0)
+        else:
+            optimizer._step = int(o["step"])
         for k in ("beta1", "beta2", "eps", "weight_decay", "momentum"):
             if k in o and hasattr(optimizer, k):
                 setattr(optimizer, k, float(o[k]))

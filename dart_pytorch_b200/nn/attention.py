@@ -262,7 +262,7 @@ class MultiHeadAttention(Module):
         H, Hkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         if q2.is_cuda and mask is None and q2.dtype == torch.bfloat16 and not q2.requires_grad:
             from ..ops import flash
-            if flash.supported_head_dim(hd):
+            if flash.kernel_head_dim(hd) == hd:
                 k2 = k3.reshape(-1, k3.shape[-1]) if k3.is_contiguous() else None
                 if k2 is not None:
                     o, _ = flash.attn_fwd(q2, k2, v3.reshape(-1, v3.shape[-1]), B, Sq, Sk, H, Hkv, hd, causal,
@@ -275,6 +275,10 @@ class MultiHeadAttention(Module):
                 o, _ = flash.attn_fwd(q2, kf, vf, B, Sq, Sk, H, Hkv, hd, causal, q_offset=q_offset, need_lse=False,
                                       kv_batch_rows=cap)
                 return o
+        if q2.is_cuda and mask is None and q2.dtype == torch.bfloat16:
+            from ..ops import flash
+            return flash.attention_tokens(q2, k3.reshape(B * Sk, Hkv * hd), v3.reshape(B * Sk, Hkv * hd), B, Sq, Sk, H,
+                                          Hkv, hd, causal, q_offset)
         q = q2.reshape(B, Sq, H, hd).transpose(1, 2)
         k = k3.reshape(B, Sk, Hkv, hd).transpose(1, 2)
         v = v3.reshape(B, Sk, Hkv, hd).transpose(1, 2)

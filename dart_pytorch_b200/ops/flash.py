@@ -36,8 +36,34 @@ class AttnBwdArgs(ctypes.Structure):
                 ("causal", c_int), ("q_offset", c_int), ("scale", c_float)]
 
 
+def kernel_head_dim(hd: int, backward: bool = False) -> Optional[int]:
+    """Head size the tensor-core kernels run a head of ``hd`` features at: 64 and 128 directly (the backward kernel
+    exists for 64 only), smaller sizes that are a multiple of 8 zero-padded to 64 (zeros add nothing to the scores and
+    give zero output columns), sizes between 64 and 128 padded to 128 in forward.  ``None`` = no kernel for it."""
+    if hd <= 0 or hd % 8:
+        return None
+    if hd <= 64:
+        return 64
+    if hd <= 128 and not backward:
+        return 128
+    return None
+
+
 def supported_head_dim(hd: int, backward: bool = False) -> bool:
-    return hd == 64 or (hd == 128 and not backward)
+    return kernel_head_dim(hd, backward) is not None
+
+
+def _wants_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(t.requires_grad for t in tensors)
+
+
+def _pad_heads(x2: torch.Tensor, heads: int, hd: int, to: int) -> torch.Tensor:
+    """Token-major ``[rows, heads*hd]`` -> ``[rows, heads*to]`` with zeros behind every head's features."""
+    return torch.nn.functional.pad(x2.reshape(x2.shape[0], heads, hd), (0, to - hd)).reshape(x2.shape[0], heads * to)
+
+
+def _to_bhsd(x2: torch.Tensor, batch: int, seq: int, heads: int, hd: int) -> torch.Tensor:
+    return x2.reshape(batch, seq, heads, hd).transpose(1, 2)
 
 
 def _ld(t: torch.Tensor) -> int:
@@ -109,36 +135,47 @@ class SeparateAttentionFn(torch.autograd.Function):
     """Attention over separate token-major ``q [B*Sq, H hd]``, ``k``/``v`` ``[B*Sk, Hkv hd]``."""
 
     @staticmethod
-    def forward(ctx, q2, k2, v2, B, Sq, Sk, H, Hkv, hd, causal, q_offset):
-        o, lse = attn_fwd(q2, k2, v2, B, Sq, Sk, H, Hkv, hd, causal, q_offset=q_offset, need_lse=True)
+    def forward(ctx, q2, k2, v2, B, Sq, Sk, H, Hkv, hd, causal, q_offset, scale=None):
+        o, lse = attn_fwd(q2, k2, v2, B, Sq, Sk, H, Hkv, hd, causal, q_offset=q_offset, scale=scale, need_lse=True)
         ctx.save_for_backward(q2, k2, v2, o, lse)
-        ctx.cfg = (B, Sq, Sk, H, Hkv, hd, causal, q_offset)
+        ctx.cfg = (B, Sq, Sk, H, Hkv, hd, causal, q_offset, scale)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q2, k2, v2, o, lse = ctx.saved_tensors
-        B, Sq, Sk, H, Hkv, hd, causal, q_offset = ctx.cfg
+        B, Sq, Sk, H, Hkv, hd, causal, q_offset, scale = ctx.cfg
         do = do if do.is_contiguous() else do.contiguous()
         dq, dk, dv = torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(v2)
-        attn_bwd(q2, k2, v2, o, do, lse, dq, dk, dv, B, Sq, Sk, H, Hkv, hd, causal, q_offset=q_offset)
-        return dq, dk, dv, None, None, None, None, None, None, None, None
+        attn_bwd(q2, k2, v2, o, do, lse, dq, dk, dv, B, Sq, Sk, H, Hkv, hd, causal, q_offset=q_offset, scale=scale)
+        return dq, dk, dv, None, None, None, None, None, None, None, None, None
 
 
 def attention_packed(qkv, batch, seq, heads, kv_heads, head_dim, causal=True):
-    if qkv.dtype != torch.bfloat16 or not supported_head_dim(head_dim):
-        x = qkv.reshape(batch, seq, -1)
-        d_q, d_kv = heads * head_dim, kv_heads * head_dim
-        q = x[..., :d_q].reshape(batch, seq, heads, head_dim).transpose(1, 2)
-        k = x[..., d_q:d_q + d_kv].reshape(batch, seq, kv_heads, head_dim).transpose(1, 2)
-        v = x[..., d_q + d_kv:].reshape(batch, seq, kv_heads, head_dim).transpose(1, 2)
-        return attention_bhsd(q, k, v, causal=causal).transpose(1, 2).reshape(batch * seq, d_q)
-    return PackedAttentionFn.apply(qkv, batch, seq, heads, kv_heads, head_dim, causal)
+    """Attention over a fused projection output ``[B*S, (H + 2 Hkv) hd]`` -> ``[B*S, H hd]``."""
+    d_q, d_kv = heads * head_dim, kv_heads * head_dim
+    hd_k = kernel_head_dim(head_dim, backward=_wants_grad(qkv)) if qkv.dtype == torch.bfloat16 else None
+    if hd_k == head_dim:
+        return PackedAttentionFn.apply(qkv, batch, seq, heads, kv_heads, head_dim, causal)
+    return attention_tokens(qkv[:, :d_q], qkv[:, d_q:d_q + d_kv], qkv[:, d_q + d_kv:], batch, seq, seq, heads, kv_heads,
+                            head_dim, causal)
 
 
 def attention_tokens(q2, k2, v2, batch, sq, sk, heads, kv_heads, head_dim, causal=True, q_offset=0):
-    """Token-major separate operands (used with a KV cache: ``k2``/``v2`` are cache views)."""
-    return SeparateAttentionFn.apply(q2, k2, v2, batch, sq, sk, heads, kv_heads, head_dim, causal, q_offset)
+    """Token-major separate operands ``q2 [B*Sq, H hd]``, ``k2`` / ``v2`` ``[B*Sk, Hkv hd]`` (with a KV cache: cache
+    views) -> ``[B*Sq, H hd]``.  bf16 heads of 64 / 128 features run the tensor-core kernels as they are, other sizes
+    zero-padded to the next of the two; what the kernels do not cover (see ``kernel_head_dim``) runs the composed path."""
+    hd_k = kernel_head_dim(head_dim, backward=_wants_grad(q2, k2, v2)) if q2.dtype == torch.bfloat16 else None
+    if hd_k is None:
+        o = _attention_composed(_to_bhsd(q2, batch, sq, heads, head_dim), _to_bhsd(k2, batch, sk, kv_heads, head_dim),
+                                _to_bhsd(v2, batch, sk, kv_heads, head_dim), causal, None, q_offset)
+        return o.transpose(1, 2).reshape(batch * sq, heads * head_dim)
+    if hd_k == head_dim:
+        return SeparateAttentionFn.apply(q2, k2, v2, batch, sq, sk, heads, kv_heads, head_dim, causal, q_offset)
+    o = SeparateAttentionFn.apply(_pad_heads(q2, heads, head_dim, hd_k), _pad_heads(k2, kv_heads, head_dim, hd_k),
+                                  _pad_heads(v2, kv_heads, head_dim, hd_k), batch, sq, sk, heads, kv_heads, hd_k, causal,
+                                  q_offset, 1.0 / math.sqrt(head_dim))
+    return o.reshape(batch * sq, heads, hd_k)[:, :, :head_dim].reshape(batch * sq, heads * head_dim)
 
 
 def attention_bhsd(q, k, v, causal=False, mask=None, q_offset=0):
@@ -147,7 +184,7 @@ def attention_bhsd(q, k, v, causal=False, mask=None, q_offset=0):
     device path: score GEMMs on the SIMT kernel, row softmax kernel."""
     B, H, Sq, hd = q.shape
     Hkv, Sk = k.shape[1], k.shape[2]
-    if q.dtype == torch.bfloat16 and mask is None and supported_head_dim(hd, backward=q.requires_grad):
+    if q.dtype == torch.bfloat16 and mask is None and supported_head_dim(hd, backward=_wants_grad(q, k, v)):
         q2 = q.transpose(1, 2).reshape(B * Sq, H * hd)
         k2 = k.transpose(1, 2).reshape(B * Sk, Hkv * hd)
         v2 = v.transpose(1, 2).reshape(B * Sk, Hkv * hd)

@@ -14,6 +14,8 @@ from .optimizer import Optimizer
 
 
 class Adam(Optimizer):
+    HYPER_SLOTS = 16
+
     def __init__(self, parameters, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
                  weight_decay: float = 0.0, weightDecay=None, arena=None, skip_nonfinite: bool = False):
         super().__init__(parameters, lr, arena)
@@ -28,7 +30,10 @@ class Adam(Optimizer):
             self.v = torch.zeros(n, dtype=torch.float32, device=dev)
             # {lr, 1-b1^t, 1-b2^t} read by the kernel from device memory, so a captured graph sees fresh values.
             self.hyper = torch.zeros(4, dtype=torch.float32, device=dev)
-            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+            # The host may queue many steps before the GPU runs the first; each step's values therefore get their own
+            # pinned slot, reused only after the copy that read it has completed (an event per slot).
+            self._hyper_ring = [torch.zeros(4, dtype=torch.float32).pin_memory() for _ in range(self.HYPER_SLOTS)]
+            self._hyper_events = [None] * self.HYPER_SLOTS
 
     @property
     def step_count(self) -> int:
@@ -38,10 +43,18 @@ class Adam(Optimizer):
         """Host half of a device step: advance ``t`` and publish {lr, bias corrections} to the device (async copy).
         Call outside a CUDA-graph capture; ``launch_step`` is the capturable half."""
         self._step += 1
-        self._hyper_host[0] = self.lr
-        self._hyper_host[1] = 1.0 - self.beta1 ** self._step
-        self._hyper_host[2] = 1.0 - self.beta2 ** self._step
-        self.hyper.copy_(self._hyper_host, non_blocking=True)
+        slot = self._step % self.HYPER_SLOTS
+        done = self._hyper_events[slot]
+        if done is not None:
+            done.synchronize()               # the copy issued HYPER_SLOTS steps ago has read this slot
+        host = self._hyper_ring[slot]
+        host[0] = self.lr
+        host[1] = 1.0 - self.beta1 ** self._step
+        host[2] = 1.0 - self.beta2 ** self._step
+        self.hyper.copy_(host, non_blocking=True)
+        done = done if done is not None else torch.cuda.Event()
+        done.record()
+        self._hyper_events[slot] = done
 
     def launch_step(self) -> None:
         from ..ops import kernels as K

@@ -92,10 +92,10 @@ class GradReducer:
                     self._launch(b)
         self._ready.clear()
 
-    def _launch(self, b: int) -> None:
+    def _launch(self, b: int, exposed: bool = False) -> None:
         self._side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self._side):
-            self.impl.reduce_bucket(b)
+            self.impl.reduce_bucket(b, exposed=exposed)
         self._launched.add(b)
 
     def _finish_overlap(self) -> None:
@@ -108,7 +108,7 @@ class GradReducer:
             self._learned = True
         for b in range(len(self.buckets)):
             if b not in self._launched:
-                self._launch(b)
+                self._launch(b, exposed=True)      # backward is over: these run alone, on the whole GPU
         torch.cuda.current_stream().wait_stream(self._side)
 
     def _fold_local_norm(self, ctrl: torch.Tensor, max_norm: float) -> None:

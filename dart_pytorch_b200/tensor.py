@@ -52,13 +52,19 @@ def _resolve_device(device, length: int) -> torch.device:
 
 
 class Tensor:
-    __slots__ = ("t", "_debug_children")
+    __slots__ = ("t", "_debug_children", "debug_node")
 
+    # Called as ``hook(step_index, tensor)`` after every backward closure of a ``backward()`` call, in execution order
+    # (reference: debugBackwardHook, lib/core/tensor/tensor.dart:42-45, fired at tensor.dart:562-563).  The tape is
+    # torch's, which keeps no handle on a node's forward result, so ``tensor`` wraps the gradient that arrived at the
+    # node (what the reference user reads as ``tensor.grad``); ``tensor.debug_node`` names the closure and
+    # ``tensor.debugChildShapes`` lists the shapes of the gradients it handed on.
     debug_backward_hook: Optional[Callable[[int, "Tensor"], None]] = None
 
     def __init__(self, t: torch.Tensor):
         self.t = t
         self._debug_children = None
+        self.debug_node = None
 
     # ---- factories -------------------------------------------------------------------------------
     @staticmethod
@@ -210,7 +216,31 @@ class Tensor:
     def backward(self, freeGraph: bool = True) -> None:
         if not self.t.requires_grad:
             raise RuntimeError("backward: tensor does not require grad")
-        self.t.backward(torch.ones_like(self.t), retain_graph=not freeGraph)
+        hook = Tensor.debug_backward_hook
+        handles = []
+        if hook is not None and self.t.grad_fn is not None:
+            counter = [0]
+            seen, stack = set(), [self.t.grad_fn]
+            while stack:
+                fn = stack.pop()
+                if fn is None or fn in seen:
+                    continue
+                seen.add(fn)
+
+                def fire(grad_inputs, grad_outputs, fn=fn):
+                    g = next((x for x in grad_outputs if x is not None), None)
+                    node = Tensor(g.detach() if g is not None else torch.zeros(()))
+                    node._debug_children = [list(x.shape) for x in grad_inputs if x is not None]
+                    node.debug_node = fn.name()
+                    hook(counter[0], node)
+                    counter[0] += 1
+                handles.append(fn.register_hook(fire))
+                stack.extend(f for f, _ in fn.next_functions)
+        try:
+            self.t.backward(torch.ones_like(self.t), retain_graph=not freeGraph)
+        finally:
+            for h in handles:
+                h.remove()
 
     def zeroGrad(self) -> None:
         self.t.grad = None

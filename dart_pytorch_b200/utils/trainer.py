@@ -35,6 +35,13 @@ class Trainer:
         self._stream = torch.cuda.Stream() if self.use_graph else None
         self.last_norm = None
         self.kernels_per_step = None
+        # Data parallel: a rank whose wait for its peers ran out poisons the step's gradient norm (NaN), so the update
+        # must be skipped on every rank alike, and the device status word is polled now and then so that the run stops
+        # with an error instead of training on with diverged replicas.
+        self.health_every = 100 if reducer is not None else 0
+        self._steps = 0
+        if reducer is not None and hasattr(optimizer, "skip_nonfinite"):
+            optimizer.skip_nonfinite = True
 
     # ---- one eager step (also what gets captured) -------------------------------------------------
     def _device_step(self, x, y, split_optimizer: bool):
@@ -83,6 +90,10 @@ class Trainer:
 
         ``x`` / ``y`` may live in (pinned) host memory: they are copied to the device asynchronously."""
         dev = self.model.device
+        self._steps += 1
+        if self.health_every and self.on_cuda and self._steps % self.health_every == 0:
+            from .. import _native
+            _native.raise_on_device_error()    # synchronises; every `health_every` steps only
         if self.on_cuda and not x.is_cuda:
             x = x.to(dev, non_blocking=True)
             y = y.to(dev, non_blocking=True)

@@ -29,7 +29,7 @@ def main():
                        activation=Activation.geluTanh, init_std=0.02, seed=5)
     model = dp.GPT(cfg).to("cuda", torch.bfloat16)
     opt = dp.Adam(model.parameters(), lr=1e-3, weight_decay=0.1)
-    red = GradReducer(opt.arena, world, mode="fused", bucket_mb=0.25)
+    red = GradReducer(opt.arena, world, mode="fused", bucket_mb=0.25, overlap=(mode == "overlap"))
     assert red.mode == "fused"
     arena = opt.arena
     # 1. raw reduction against an fp32 reference
@@ -58,6 +58,26 @@ def main():
         other = mine.clone()
         dist.broadcast(other, 0)
         assert torch.equal(mine.view(torch.int16), other.view(torch.int16))
+    # 1b. one rank reaches the reduction late (its host was busy for longer than a pipeline wait lasts): the others
+    #     wait for it inside the kernel, up to the reducer's skew limit, and the result is still the exact average
+    if mode == "late":
+        import time
+        g = torch.Generator(device="cuda").manual_seed(900 + rank)
+        local_grad = (torch.randn(arena.numel, device="cuda", generator=g) * 0.01).bfloat16()
+        arena.grad.copy_(local_grad)
+        ref = local_grad.float()
+        dist.all_reduce(ref)
+        ref = ref / world
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == world - 1:
+            time.sleep(1.6)
+        ctrl = torch.zeros(4, device="cuda")
+        red.reduce(ctrl, 1.0)
+        torch.cuda.synchronize()
+        _native.raise_on_device_error()
+        assert float(ctrl[2]) == 1.0
+        assert float((arena.grad.float() - ref).norm() / ref.norm()) < 5e-3
     # 2. a few training steps: replicas must stay bit-identical
     trainer = Trainer(model, opt, None, clip_norm=1.0, reducer=red, use_graph=(mode != "nograph"))
     gen = torch.Generator().manual_seed(7 + rank)

@@ -34,6 +34,8 @@ FWD_CASES = [
     (1, 128, 1, 1, 64, False), (1, 128, 1, 1, 64, True), (2, 256, 2, 2, 64, True), (2, 384, 3, 3, 64, True),
     (2, 1024, 4, 4, 64, True), (3, 197, 2, 2, 64, False), (1, 300, 2, 1, 64, True), (2, 512, 4, 2, 64, False),
     (1, 128, 1, 1, 128, True), (2, 256, 4, 1, 128, True), (1, 1000, 2, 2, 128, False),
+    # head sizes the kernels take zero-padded to 64 / 128
+    (2, 200, 4, 4, 32, True), (1, 96, 2, 1, 16, True), (2, 64, 2, 2, 8, False), (1, 256, 2, 2, 96, True),
 ]
 
 
@@ -68,7 +70,9 @@ def test_attention_forward_q_offset():
 
 
 BWD_CASES = [(1, 128, 1, 1, 64, False), (1, 128, 1, 1, 64, True), (2, 256, 2, 2, 64, True), (2, 640, 3, 3, 64, True),
-             (3, 197, 2, 2, 64, False), (1, 300, 4, 2, 64, True), (2, 1024, 2, 2, 64, True)]
+             (3, 197, 2, 2, 64, False), (1, 300, 4, 2, 64, True), (2, 1024, 2, 2, 64, True),
+             # padded head sizes (kernel at 64), and 128, which has no backward kernel and takes the composed path
+             (2, 200, 4, 4, 32, True), (1, 96, 4, 2, 16, True), (2, 40, 2, 2, 8, False), (1, 128, 4, 1, 128, True)]
 
 
 @pytest.mark.parametrize("B,S,H,Hkv,hd,causal", BWD_CASES)
@@ -86,3 +90,66 @@ def test_attention_backward(B, S, H, Hkv, hd, causal):
     for name, sl in (("dq", slice(0, dq_)), ("dk", slice(dq_, dq_ + dkv_)), ("dv", slice(dq_ + dkv_, None))):
         assert torch.isfinite(qkv.grad[:, sl].float()).all(), name
         assert _rel(qkv.grad[:, sl], x.grad[:, sl]) < 3e-2, name
+
+
+def _launches():
+    import ctypes
+    from dart_pytorch_b200 import _native
+    lib = _native.load(required=True)
+    lib.dptb_launch_count.restype = ctypes.c_longlong
+    return lib.dptb_launch_count()
+
+
+@pytest.mark.parametrize("hd,heads,kv_heads", [(32, 4, 4), (128, 2, 1), (64, 2, 2), (16, 4, 2)])
+def test_self_attention_module_gradients(hd, heads, kv_heads):
+    """bf16 ``MultiHeadAttention`` on the GPU against the same module in fp32 on the CPU, output and every gradient,
+    for head sizes with a backward kernel (64, and 16 / 32 padded) and without one (128)."""
+    from dart_pytorch_b200.nn.attention import MultiHeadAttention
+    D = hd * heads
+    torch.manual_seed(0)
+    ref = MultiHeadAttention(D, heads, num_kv_heads=kv_heads, bias=True, seed=3)
+    dev = MultiHeadAttention(D, heads, num_kv_heads=kv_heads, bias=True, seed=3).to("cuda", torch.bfloat16)
+    x = torch.randn(2, 48, D)
+    xr = x.clone().requires_grad_(True)
+    xd = x.to("cuda", torch.bfloat16).requires_grad_(True)
+    yr = ref(xr, causal=True)
+    yd = dev(xd, causal=True)
+    assert _rel(yd.cpu(), yr) < 3e-2
+    g = torch.randn_like(yr)
+    yr.backward(g)
+    yd.backward(g.to("cuda", torch.bfloat16))
+    assert _rel(xd.grad.cpu(), xr.grad) < 5e-2
+    for pd, pr in zip(dev.parameters(), ref.parameters()):
+        assert pd.grad is not None and _rel(pd.grad.cpu(), pr.grad) < 5e-2
+
+
+@pytest.mark.parametrize("hd", [32, 128, 64])
+def test_cross_attention_module_gradients(hd):
+    from dart_pytorch_b200.nn.attention import MultiHeadCrossAttention
+    heads = 2
+    D = hd * heads
+    ref = MultiHeadCrossAttention(D, 48, heads, bias=True, seed=5)
+    dev = MultiHeadCrossAttention(D, 48, heads, bias=True, seed=5).to("cuda", torch.bfloat16)
+    torch.manual_seed(1)
+    xq, xkv = torch.randn(2, 40, D), torch.randn(2, 24, 48)
+    xqr, xkvr = xq.clone().requires_grad_(True), xkv.clone().requires_grad_(True)
+    xqd = xq.to("cuda", torch.bfloat16).requires_grad_(True)
+    xkvd = xkv.to("cuda", torch.bfloat16).requires_grad_(True)
+    yr, yd = ref(xqr, xkvr), dev(xqd, xkvd)
+    assert _rel(yd.cpu(), yr) < 3e-2
+    g = torch.randn_like(yr)
+    yr.backward(g)
+    yd.backward(g.to("cuda", torch.bfloat16))
+    assert _rel(xqd.grad.cpu(), xqr.grad) < 5e-2
+    assert _rel(xkvd.grad.cpu(), xkvr.grad) < 5e-2
+
+
+def test_small_heads_run_the_flash_kernels():
+    """A head size of 32 must reach ``attn_fwd_kernel`` / ``attn_bwd_kernel`` (padded), not the composed path: the
+    composed path launches a GEMM and a softmax per (batch, head), the kernels a handful in total."""
+    B, S, H, hd = 2, 128, 8, 32
+    qkv = _qkv(B, S, H, H, hd).requires_grad_(True)
+    before = _launches()
+    o = A.attention_packed(qkv, B, S, H, H, hd, True)
+    o.backward(torch.ones_like(o))
+    assert _launches() - before <= 6

@@ -19,11 +19,33 @@ def _run(mode: str, nproc: int = 2, port: int = 29533):
     assert "dp_worker ok" in proc.stdout
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_allreduce_peer_loads():
-    _run("p2p", port=29533)
+def _worlds():
+    """Rank counts to test: 2, 4 and 8 as far as the machine has GPUs."""
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return [w for w in (2, 4, 8) if w <= n] or [2]
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_allreduce_auto_multimem():
-    _run("auto", port=29534)
+needs2 = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_allreduce_peer_loads(world):
+    _run("p2p", nproc=world, port=29533)
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_allreduce_auto_multimem(world):
+    _run("auto", nproc=world, port=29534)
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_allreduce_overlapped_with_backward(world):
+    _run("overlap", nproc=world, port=29535)
+
+
+@needs2
+def test_fused_allreduce_tolerates_a_late_rank():
+    _run("late", nproc=2, port=29536)

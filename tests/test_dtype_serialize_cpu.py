@@ -245,3 +245,26 @@ def test_small_api_parity_items(tmp_path, monkeypatch):
     monkeypatch.setenv("DPTB200_NATIVE_LIB", str(tmp_path / "missing.so"))
     with pytest.raises(_native.NativeLibraryError):
         _native.ensureNativeLib()
+
+
+def test_debug_backward_hook_fires_after_every_closure():
+    """``Tensor.debug_backward_hook`` is called with a running index and a view of each backward node, in execution
+    order, and is silent once removed."""
+    from dart_pytorch_b200.tensor import Tensor
+    a = Tensor.fromList([2, 3], [1, 2, 3, 4, 5, 6], requiresGrad=True)
+    w = Tensor.fromList([3, 2], [0.5, -1, 2, 0.25, 1, 1], requiresGrad=True)
+    seen = []
+    Tensor.debug_backward_hook = lambda i, t: seen.append((i, t.debug_node, list(t.shape)))
+    try:
+        (a.matmul(w).tanh() * 2.0).sum().backward()
+    finally:
+        Tensor.debug_backward_hook = None
+    assert [i for i, _, _ in seen] == list(range(len(seen))) and len(seen) >= 5
+    names = [n for _, n, _ in seen]
+    assert any("Tanh" in n for n in names) and any("Mm" in n or "Matmul" in n.title() for n in names)
+    assert names.index(next(n for n in names if "Tanh" in n)) < names.index(next(n for n in names if "Mm" in n))
+    assert a.grad is not None and w.grad is not None
+    n = len(seen)
+    b = Tensor.fromList([2], [1.0, 2.0], requiresGrad=True)
+    (b * b).sum().backward()
+    assert len(seen) == n

@@ -116,3 +116,32 @@ def test_llama_loss_and_grads_match_cpu_reference():
         num = (pg.grad.float().cpu() - pc.grad).norm()
         den = pc.grad.norm() + 1e-8
         assert float(num / den) < 8e-2, (tuple(pc.shape), float(num / den))
+
+
+def test_adam_steps_queued_without_sync_use_their_own_hyperparameters():
+    """The host may run many steps ahead of the GPU (loss never read): each queued step must still see the learning
+    rate and bias corrections of its own step number.  A long spin kernel holds the stream while 24 steps with a
+    changing learning rate are queued; the result is compared with the same steps in float64 on the host."""
+    import dart_pytorch_b200 as dp
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(4096, device="cuda"))
+    opt = dp.Adam([p], lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
+    assert opt.arena is not None
+    grads = [torch.randn(4096, device="cuda") for _ in range(24)]
+    lrs = [1e-2 * (1 + i) / 8 for i in range(24)]
+    w = p.detach().double().cpu().clone()
+    m, v = torch.zeros_like(w), torch.zeros_like(w)
+    torch.cuda.synchronize()
+    torch.cuda._sleep(400_000_000)              # ~0.2 s of device time ahead of everything queued below
+    for g, lr in zip(grads, lrs):
+        p.grad.copy_(g)
+        opt.lr = lr
+        opt.step()
+    torch.cuda.synchronize()
+    for t, (g, lr) in enumerate(zip(grads, lrs), start=1):
+        g = g.double().cpu()
+        m = 0.9 * m + 0.1 * g
+        v = 0.95 * v + 0.05 * g * g
+        upd = lr * (m / (1 - 0.9 ** t)) / ((v / (1 - 0.95 ** t)).sqrt() + 1e-8) + lr * 0.1 * w
+        w = w - upd
+    assert torch.allclose(p.detach().double().cpu(), w, rtol=1e-4, atol=1e-5)

@@ -253,3 +253,40 @@ def test_clip_grad_norm_cases():
     with pytest.raises(ValueError):
         clip_grad_norm([a], 0.0)
     assert float(clip_grad_norm([c], 1.0)) == 0.0
+
+
+def test_sgd_momentum_survives_a_save_and_resume(tmp_path):
+    """SGD keeps its momentum per parameter; the sidecar must carry it (and the step count, because the first SGD
+    step overwrites the momentum with the gradient), so that a resumed run equals the uninterrupted one."""
+    import dart_pytorch_b200 as dp
+    from dart_pytorch_b200.io.dptc import Checkpoint
+    from dart_pytorch_b200.io.train_state import load_train_state, save_train_state
+    from dart_pytorch_b200.models import GPT, GPTConfig
+
+    def make():
+        m = GPT(GPTConfig(vocab_size=29, max_ctx=10, embed_dim=16, num_layers=1, num_heads=2, seed=9))
+        return m, dp.SGD(m.parameters(), lr=5e-2, momentum=0.9, weight_decay=0.01)
+
+    def run(m, o, steps, g):
+        for _ in range(steps):
+            x = torch.randint(0, 29, (2, 10), generator=g)
+            o.zero_grad()
+            m.loss(x[:, :-1], x[:, 1:]).backward()
+            o.step()
+
+    g = torch.Generator().manual_seed(1)
+    m1, o1 = make()
+    run(m1, o1, 3, g)
+    Checkpoint.save_file(m1, str(tmp_path / "s.dptc"))
+    save_train_state(str(tmp_path / "s.dpts"), o1)
+    gstate = g.get_state()
+    run(m1, o1, 3, g)
+    m2, o2 = make()
+    Checkpoint.load_into_file(m2, str(tmp_path / "s.dptc"))
+    load_train_state(str(tmp_path / "s.dpts"), o2, restore_rng=False)
+    assert o2._steps == 3 and len(o2._velocity) == len(o2.parameters)
+    g2 = torch.Generator()
+    g2.set_state(gstate)
+    run(m2, o2, 3, g2)
+    for a, b in zip(m1.parameters(), m2.parameters()):
+        assert torch.allclose(a, b, atol=1e-6)

@@ -19,23 +19,36 @@ def _run(script: str, mode: str, nproc: int = 2, port: int = 29543, ok: str = "o
     assert ok in proc.stdout
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_gemm_allreduce_peer_loads():
-    _run("tp_worker.py", "p2p", port=29543, ok="tp_worker ok")
+def _worlds():
+    """Rank counts to test: 2, 4 and 8 as far as the machine has GPUs."""
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return [w for w in (2, 4, 8) if w <= n] or [2]
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fused_gemm_allreduce_auto_multimem():
-    _run("tp_worker.py", "auto", port=29544, ok="tp_worker ok")
+needs2 = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_gemm_allreduce_peer_loads(world):
+    _run("tp_worker.py", "p2p", nproc=world, port=29543, ok="tp_worker ok")
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_fused_gemm_allreduce_auto_multimem(world):
+    _run("tp_worker.py", "auto", nproc=world, port=29544, ok="tp_worker ok")
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("hd", ["64", "128"])
-def test_tp_llama_engine_matches_whole_model(hd):
-    _run("tp_llama_worker.py", hd, port=29545 + (hd == "128"), ok="tp_llama_worker ok")
+def test_tp_llama_engine_matches_whole_model(hd, world):
+    _run("tp_llama_worker.py", hd, nproc=world, port=29545 + (hd == "128"), ok="tp_llama_worker ok")
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@needs2
+@pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("cf", ["1.25", "0.5"])
-def test_expert_parallel_moe_matches_dense_reference(cf):
-    _run("ep_worker.py", cf, port=29551 + (cf == "0.5"), ok="ep_worker ok")
+def test_expert_parallel_moe_matches_dense_reference(cf, world):
+    _run("ep_worker.py", cf, nproc=world, port=29551 + (cf == "0.5"), ok="ep_worker ok")

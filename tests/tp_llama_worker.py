@@ -24,8 +24,9 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     hd = int(sys.argv[1]) if len(sys.argv) > 1 else 64
-    cfg = LlamaConfig(vocab_size=512, max_ctx=96, embed_dim=4 * hd, num_layers=2, num_heads=4, num_kv_heads=2,
-                      ffn_dim=512, rope_base=10000.0, tie_weights=False, seed=3, init_std=0.05)
+    heads, kv_heads = (4, 2) if world <= 2 else (2 * world, world)     # every rank owns at least one KV head
+    cfg = LlamaConfig(vocab_size=512, max_ctx=96, embed_dim=heads * hd, num_layers=2, num_heads=heads,
+                      num_kv_heads=kv_heads, ffn_dim=512 if world <= 4 else 1024, rope_base=10000.0, tie_weights=False, seed=3, init_std=0.05)
     ref = Llama(cfg).to("cuda", torch.bfloat16)          # same seed -> same weights on every rank
     ref.eval()
     eng = TPLlamaEngine(cfg, max_batch=4, max_ctx=96, max_rows=4 * 40, full_model=ref)
