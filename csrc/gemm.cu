@@ -437,6 +437,26 @@ __device__ __forceinline__ void add_row64(float (&v)[64], const uint4 (&t)[8]) {
     for (int e = 0; e < 8; ++e) v[g * 8 + e] += f[e];
   }
 }
+// Tensor maps of the tile-store epilogue (32-row x 64-column bf16 boxes, 128-byte swizzle): the output, the optional
+// pre-activation copy, and the one optional per-element input (activation input, residual, or C itself when
+// accumulating).  Unused maps are copies of the output's.
+struct EpiMaps {
+  CUtensorMap c, aux, in;
+};
+// One thread's 128-byte row of a staged 32 x 64 block, 16-byte chunks XOR-swizzled by row as the tile copies expect.
+__device__ __forceinline__ void st_smem_row64(uint8_t* buf, int lane, const uint4 (&v)[8]) {
+  uint8_t* row = buf + lane * 128;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) *reinterpret_cast<uint4*>(row + ((g ^ (lane & 7)) << 4)) = v[g];
+}
+__device__ __forceinline__ void ld_smem_row64(const uint8_t* buf, int lane, uint4 (&v)[8]) {
+  const uint8_t* row = buf + lane * 128;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) v[g] = *reinterpret_cast<const uint4*>(row + ((g ^ (lane & 7)) << 4));
+}
+// Wait until at most one of this thread's tile stores is still reading its shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
 // Requests the first per-element input of the block (and the bias slice) before the accumulator load is waited for.
 __device__ __forceinline__ void epi_prefetch(const GemmParams& p, uint32_t* bias_s, long long row, long long col0,
                                              int lane, EpiIn& in) {
@@ -454,9 +474,14 @@ __device__ __forceinline__ void epi_prefetch(const GemmParams& p, uint32_t* bias
   }
   if (p.bias) bias_s[lane] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col0) + lane);
 }
+// TMA = true: outputs leave through shared memory and one tile store per block (`buf_aux` / `buf_c`: 4 KB staging
+// blocks of this warp, `em`: the tensor maps); the caller has made `buf_aux` free, and this function frees `buf_c`
+// (waits for the store that last read it) before writing it.  Rows and columns outside the matrix are clipped by the copy.
+template <bool TMA = false>
 __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32_t* bias_s, long long row0,
                                                long long col0, int lane, const uint32_t (&r0)[32],
-                                               const uint32_t (&r1)[32], const EpiIn& in) {
+                                               const uint32_t (&r1)[32], const EpiIn& in, uint8_t* buf_aux = nullptr,
+                                               uint8_t* buf_c = nullptr, const EpiMaps* em = nullptr) {
   const long long row = row0 + lane;
   const bool live = row < p.M;
   const bool wide = p.row_epi == 2;
@@ -482,7 +507,19 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
     uint4 o[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
-    if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
+    if constexpr (TMA) {
+      st_smem_row64(buf_aux, lane, o);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(&em->aux, buf_aux, (int)col0, (int)row0);
+        bulk_commit_group();
+        bulk_wait_read_1();     // the store before this one (which read buf_c) has finished reading
+      }
+      __syncwarp();
+    } else {
+      if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
+    }
   }
   if (p.act == 2) {
     // GELU (tanh form), the one activation on the training hot path, outside the per-group dispatch: five
@@ -546,7 +583,17 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
   uint4 o[8];
 #pragma unroll
   for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
-  if (live) st_row64(static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0, wide, o);
+  if constexpr (TMA) {
+    st_smem_row64(buf_c, lane, o);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(&em->c, buf_c, (int)col0, (int)row0);
+      bulk_commit_group();
+    }
+  } else {
+    if (live) st_row64(static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0, wide, o);
+  }
 }
 
 // ----------------------------------------------------------------------------- all-reduce epilogue helpers
@@ -640,14 +687,18 @@ constexpr int kBK = 64;
 constexpr int kEpiWarps = 8;
 constexpr int kGemmThreads = 32 * (2 + kEpiWarps);
 
-template <int BN, int STAGES>
+// BROWS: rows (K-major) or columns (MN-major) of B one CTA stages: BN, or BN / 2 when a CTA pair shares the tile.
+// EPI_BLOCKS: 4 KB staging blocks per epilogue warp (two for the tile-store epilogue, which keeps one store in flight).
+template <int BN, int STAGES, int BROWS = BN, int EPI_BLOCKS = 1>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageOff = STAGES * (kABytes + kBBytes);   // epilogue staging: 4 KB per epilogue warp
-  static constexpr int kBiasOff = kStageOff + kEpiWarps * 4096;    // 64 bf16 bias values per epilogue warp
+  static constexpr int kBBytes = BROWS * kBK * 2;
+  static constexpr int kStagePerWarp = EPI_BLOCKS * 4096;
+  static constexpr int kStageOff = STAGES * (kABytes + kBBytes);   // epilogue staging
+  static constexpr int kBiasOff = kStageOff + kEpiWarps * kStagePerWarp;   // 64 bf16 bias values per epilogue warp
   static constexpr int kBarOffset = kBiasOff + kEpiWarps * 128;
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1) * 8 + 32 + 1024;  // + alignment slack
+  // barriers: full / empty per stage, 2 + 2 accumulator, 1 drain, 1 epilogue-input per epilogue warp
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1 + kEpiWarps) * 8 + 32 + 1024;  // + alignment slack
   static_assert(kTotal <= 227 * 1024, "GEMM: shared memory budget");
 };
 
@@ -656,11 +707,18 @@ struct NoPeerMaps {};
 template <bool AG> struct PeerMaps { using type = NoPeerMaps; };
 template <> struct PeerMaps<true> { using type = TmapSet; };
 
-template <bool A_MN, bool B_MN, int BN, int STAGES, bool AG = false>
+// PAIR: the kernel is launched as clusters of two CTAs that share 256-row tiles (cta_group::2): CTA r of a pair stages
+// rows [128 r, 128 r + 128) of the A tile and columns [BN/2 r, BN/2 r + BN/2) of the B tile, the leader's (r = 0)
+// issuer thread runs the MMAs of both tensor cores, each CTA's epilogue warps drain their own 128 x BN accumulator.
+// Work units are then pairs of row tiles; `tile` below stays the index of this CTA's own 128-row tile.
+template <bool A_MN, bool B_MN, int BN, int STAGES, bool AG = false, bool PAIR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ typename PeerMaps<AG>::type peers, const GemmParams p) {
-  using L = GemmSmem<BN, STAGES>;
+               const __grid_constant__ typename PeerMaps<AG>::type peers, const __grid_constant__ EpiMaps em,
+               const GemmParams p) {
+  static_assert(!(PAIR && AG), "the all-gather prologue runs on single CTAs");
+  constexpr int BROWS = PAIR ? BN / 2 : BN;
+  using L = GemmSmem<BN, STAGES, BROWS, PAIR ? 2 : 1>;
   constexpr int TMEM_COLS = 2 * BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -671,15 +729,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* drain_bar = tmem_empty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* epi_in_bar = drain_bar + 1;            // [kEpiWarps]: input block of the tile-store epilogue has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_in_bar + kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* epi_ctr = reinterpret_cast<int*>(tmem_slot + 2);       // arrival counter of the epilogue-warp barrier
   volatile int* epi_last = reinterpret_cast<volatile int*>(tmem_slot + 3);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;
+  // Row tiles are handed out singly, or in pairs (the last pair of an odd count has a second half without rows: that
+  // CTA stages zeros and its epilogue writes nothing).
+  const int sched_tiles_m = PAIR ? (p.tiles_m + 1) / 2 : p.tiles_m;
+  const int num_tiles = sched_tiles_m * p.tiles_n;
   const int num_units = num_tiles * p.splits;
+  const int unit0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int unit_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   // Launch number of the all-reduce protocol; the word is rewritten only by the last CTA to leave.
   const uint32_t ar_epoch = p.ar.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.ar.epoch) + 1u : 0u;
 
@@ -698,16 +763,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       for (int a = 0; a < 2; ++a) {
         mbar_init(&tmem_full[a], 1);
-        mbar_init(&tmem_empty[a], kEpiWarps);
+        mbar_init(&tmem_empty[a], PAIR ? 2 * kEpiWarps : kEpiWarps);   // the leader's is released by both CTAs
       }
       mbar_init(drain_bar, 1);
+      for (int w = 0; w < kEpiWarps; ++w) mbar_init(&epi_in_bar[w], 1);
       mbar_fence_init();
     }
     __syncwarp();
-    tmem_alloc<TMEM_COLS>(tmem_slot);
+    if constexpr (PAIR) tmem_alloc_pair<TMEM_COLS>(tmem_slot);
+    else tmem_alloc<TMEM_COLS>(tmem_slot);
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before either signals the other's
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -721,13 +789,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       (void)ag_epoch;
       DPTB_PROF_DECL(prof_wait);
       DPTB_PROF_BEGIN(prof_t_all);
-      for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x) {
-        const int tile = unit % num_tiles;
+      // Pair: both CTAs' copies count on the LEADER's full barrier (it expects the bytes of both).
+      uint32_t full_addr[STAGES];
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) full_addr[s] = PAIR ? map_to_cta(&full_bar[s], 0) : smem_u32(&full_bar[s]);
+      for (int unit = unit0; unit < num_units && !*abort_flag; unit += unit_step) {
+        const int stile = unit % num_tiles;
         const int kb0 = (unit / num_tiles) * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        const int mi = tile_row_index(p, tile);
+        const int mi = PAIR ? (stile % sched_tiles_m) * 2 + (int)cta_rank : tile_row_index(p, stile);
         const int m0 = mi * kBM;
-        const int n0 = (tile / p.tiles_m) * BN;
+        const int n0 = (stile / sched_tiles_m) * BN + (PAIR ? (int)cta_rank * BROWS : 0);
         const CUtensorMap* a_map = &tmA;
         int a_row = m0;
         if constexpr (AG) {
@@ -750,26 +822,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           DPTB_PROF_BEGIN(prof_t0);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) break;
           DPTB_PROF_END(prof_t0, prof_wait);
-          mbar_arrive_expect_tx(&full_bar[s], L::kABytes + L::kBBytes);
           uint8_t* a_dst = sA + s * L::kABytes;
           uint8_t* b_dst = sB + s * L::kBBytes;
-          if (A_MN) {
+          if constexpr (PAIR) {
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * (L::kABytes + L::kBBytes));
+            if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + j * 64, kb * kBK);
-          } else {
-            tma_load_2d(a_dst, a_map, &full_bar[s], kb * kBK, a_row);
-          }
-          if (B_MN) {
+              for (int j = 0; j < kBM / 64; ++j)
+                tma_load_2d_pair(a_dst + j * 8192, &tmA, full_addr[s], m0 + j * 64, kb * kBK);
+            } else {
+              tma_load_2d_pair(a_dst, &tmA, full_addr[s], kb * kBK, m0);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, kb * kBK);
+              for (int j = 0; j < BROWS / 64; ++j)
+                tma_load_2d_pair(b_dst + j * 8192, &tmB, full_addr[s], n0 + j * 64, kb * kBK);
+            } else {
+              tma_load_2d_pair(b_dst, &tmB, full_addr[s], kb * kBK, n0);
+            }
           } else {
-            tma_load_2d(b_dst, &tmB, &full_bar[s], kb * kBK, n0);
+            mbar_arrive_expect_tx(&full_bar[s], L::kABytes + L::kBBytes);
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < kBM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tmA, &full_bar[s], m0 + j * 64, kb * kBK);
+            } else {
+              tma_load_2d(a_dst, a_map, &full_bar[s], kb * kBK, a_row);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmB, &full_bar[s], n0 + j * 64, kb * kBK);
+            } else {
+              tma_load_2d(b_dst, &tmB, &full_bar[s], kb * kBK, n0);
+            }
           }
         }
       }
       DPTB_PROF_STORE(0, prof_wait);
       DPTB_PROF_STORE(1, clock64() - prof_t_all);
-      if (*abort_flag) {
+      if (PAIR && *abort_flag && cta_rank != 0) {
+        // The second CTA's copies are counted on the leader's barriers, which it cannot poll: give copies in flight
+        // (microseconds) time to land before this CTA may leave.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+      } else if (*abort_flag) {
         // Do not leave while a tile copy may still be writing this CTA's shared memory.
         const uint32_t n = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
         for (uint32_t j = 0; j < n; ++j) {
@@ -786,15 +881,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, A_MN, B_MN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 2 * kBM : kBM, BN, A_MN, B_MN);
+      // Pair: a completion is signalled to the same barrier of both CTAs by one commit.
       uint32_t consumed = 0;
       uint32_t local_tile = 0;
       bool issued_any = false;
       DPTB_PROF_DECL(prof_wait_full);
       DPTB_PROF_DECL(prof_wait_acc);
       DPTB_PROF_BEGIN(prof_t_all);
-      for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
+      for (int unit = unit0; unit < num_units && !*abort_flag; unit += unit_step, ++local_tile) {
         const int kb0 = (unit / num_tiles) * p.kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + p.kb_per_split);
         const uint32_t acc = local_tile & 1;
@@ -818,20 +914,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int k = 0; k < kBK / 16; ++k) {
             const uint64_t da = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024) : make_smem_desc(a_addr + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024) : make_smem_desc(b_addr + k * 32, 16, 1024);
-            umma_bf16(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            if constexpr (PAIR) umma_bf16_pair(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            else umma_bf16(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           issued_any = true;
-          umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+          if constexpr (PAIR) {       // stage reusable (in both CTAs) once these MMAs have read it
+            umma_commit_pair_both(&empty_bar[s]);
+          } else {
+            umma_commit(&empty_bar[s]);
+          }
         }
         if (!ok) break;
-        umma_commit(&tmem_full[acc]);  // accumulator complete
+        if constexpr (PAIR) {         // accumulator complete (each CTA's half)
+          umma_commit_pair_both(&tmem_full[acc]);
+        } else {
+          umma_commit(&tmem_full[acc]);
+        }
       }
       DPTB_PROF_STORE(2, prof_wait_full);
       DPTB_PROF_STORE(3, prof_wait_acc);
       DPTB_PROF_STORE(4, clock64() - prof_t_all);
       DPTB_PROF_STORE(7, local_tile);
       if (*abort_flag && issued_any) {
-        umma_commit(drain_bar);
+        if constexpr (PAIR) umma_commit_pair(smem_u32(drain_bar));
+        else umma_commit(drain_bar);
         uint64_t t0 = global_timer_ns();
         while (!mbar_try_wait(drain_bar, 0)) {
           if (global_timer_ns() - t0 > kWaitLimitNs / 4) {
@@ -846,8 +952,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int ew = warp - 2;
     const int q = warp & 3;      // TMEM lane quarter this warp may read
     const int half = ew >> 2;    // takes the 64-column chunks with this parity
-    uint8_t* stage = smem + L::kStageOff + ew * 4096;
+    uint8_t* stage = smem + L::kStageOff + ew * L::kStagePerWarp;
     uint32_t local_tile = 0;
+    uint32_t epi_blk = 0;        // blocks this warp has stored through the tile-store epilogue
+    uint32_t epi_in_ph = 0;      // phase of this warp's input barrier
     int epi_gen = 0;
     // Registers of one 64-column chunk of this thread's row -> final epilogue (staged bf16 path or direct fp32 path).
     auto emit = [&](long long row0, long long col0, const uint32_t (&r0)[32], const uint32_t (&r1)[32]) {
@@ -926,17 +1034,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     DPTB_PROF_DECL(prof_fin);
     DPTB_PROF_DECL(prof_blocks);
     DPTB_PROF_BEGIN(prof_t_all);
-    for (int unit = blockIdx.x; unit < num_units && !*abort_flag; unit += gridDim.x, ++local_tile) {
-      const int tile = unit % num_tiles;
+    // The accumulator is handed back to the issuer: in a pair, to the leader's barrier, by both CTAs.
+    const uint32_t tmem_empty_addr[2] = {PAIR ? map_to_cta(&tmem_empty[0], 0) : 0u,
+                                         PAIR ? map_to_cta(&tmem_empty[1], 0) : 0u};
+    auto release_acc = [&](uint32_t acc) {
+      if constexpr (PAIR) mbar_arrive_cluster(tmem_empty_addr[acc]);
+      else mbar_arrive(&tmem_empty[acc]);
+    };
+    for (int unit = unit0; unit < num_units && !*abort_flag; unit += unit_step, ++local_tile) {
+      const int stile = unit % num_tiles;
       const int split = unit / num_tiles;
-      const int m0 = tile_row_index(p, tile) * kBM;
-      const int n0 = (tile / p.tiles_m) * BN;
+      const int mi = PAIR ? (stile % sched_tiles_m) * 2 + (int)cta_rank : tile_row_index(p, stile);
+      const int ni = stile / sched_tiles_m;
+      const int tile = PAIR ? ni * p.tiles_m + mi : stile;   // this CTA's own 128-row tile (workspace / counter index)
+      const int m0 = mi * kBM;
+      const int n0 = ni * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
+      // Tile-store epilogue: this warp's bias slices are requested before the wait for the accumulator.
+      uint32_t bias_pf[BN / 128] = {};
+      if constexpr (PAIR) {
+        if (p.row_epi == 3 && p.bias && mi < p.tiles_m) {
+#pragma unroll
+          for (int j = 0; j < BN / 128; ++j) {
+            const long long col = (long long)n0 + (half + 2 * j) * 64 + 2 * lane;
+            if (col < p.N)
+              bias_pf[j] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col));
+          }
+        }
+      }
       DPTB_PROF_BEGIN(prof_t0);
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout))) break;
       DPTB_PROF_END(prof_t0, prof_wait_acc);
       tc_fence_after_sync();
+      if (PAIR && mi >= p.tiles_m) {   // second half of the last, odd pair: no rows to write
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) release_acc(acc);
+        continue;
+      }
       const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       if (p.ar.world > 0) {
@@ -965,7 +1101,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);   // the issuer may start the next tile in this accumulator
+        if (lane == 0) release_acc(acc);   // the issuer may start the next tile in this accumulator
         if (!epi_sync()) break;                          // every epilogue warp has written its blocks
         const int owner = p.ar.mode == 1 ? m0 / p.ar.rows_per_rank : tile % p.ar.world;
         if (ew == 0 && lane == 0)
@@ -980,6 +1116,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           ar_tile[ar_pending++] = tile;
         }
+      } else if (PAIR && p.splits == 1 && p.row_epi == 3) {
+        // Tile-store epilogue: registers -> swizzled staging block -> one tile store per 32 x 64 block, with the
+        // per-element input (if any) fetched into the same block by a tile load while the accumulator is read.
+        const int in_kind = p.act >= 11 ? 1 : (p.residual ? 2 : (p.accumulate ? 3 : 0));
+        const bool rows_live = row0 < p.M;   // warp-uniform
+        bool ok = true;
+#pragma unroll 1
+        for (int j = 0; j < BN / 128 && ok; ++j) {
+          const int c = half + 2 * j;
+          const long long col0 = (long long)n0 + c * 64;
+          if (col0 >= p.N || !rows_live) break;  // warp-uniform
+          uint8_t* buf_aux = stage;
+          uint8_t* buf_c = stage + (p.aux_out ? 4096 : (int)(epi_blk & 1) * 4096);
+          DPTB_PROF_BEGIN(prof_c0);
+          if (lane == 0) {
+            bulk_wait_read_1();   // the store that last read the block about to be overwritten has finished reading
+            if (in_kind) {
+              mbar_arrive_expect_tx(&epi_in_bar[ew], 4096);
+              tma_load_2d(buf_c, &em.in, &epi_in_bar[ew], (int)col0, (int)row0);
+            }
+          }
+          __syncwarp();
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_row + c * 64, r0);
+          tmem_ld_32x32(t_row + c * 64 + 32, r1);
+          if (p.bias) bias_s[lane] = bias_pf[j];
+          EpiIn in;
+          in.kind = in_kind;
+          tmem_ld_wait();
+          if (in_kind) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&epi_in_bar[ew], epi_in_ph, abort_flag, kWaitFullTimeout));
+            epi_in_ph ^= 1;
+            if (!ok) break;
+            ld_smem_row64(buf_c, lane, in.v);
+          }
+          DPTB_PROF_END(prof_c0, prof_ld);
+          DPTB_PROF_BEGIN(prof_c1);
+          epi_finish_row<true>(p, bias_s, row0, col0, lane, r0, r1, in, buf_aux, buf_c, &em);
+          DPTB_PROF_END(prof_c1, prof_fin);
+          ++epi_blk;
+#ifdef DPTB_GEMM_PROFILE
+          ++prof_blocks;
+#endif
+        }
+        if (!ok) break;
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) release_acc(acc);
       } else if (p.splits == 1) {
 #pragma unroll 1
         for (int c = half; c < BN / 64; c += 2) {
@@ -1010,7 +1194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (lane == 0) release_acc(acc);
       } else {
         // Partial accumulator -> workspace, column-major inside the tile so that a warp writes 128 contiguous bytes.
         float* wtile = p.ws + (size_t)tile * p.splits * (BN * kBM);
@@ -1030,7 +1214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        if (lane == 0) release_acc(acc);
         __threadfence();
         if (!epi_sync()) break;
         if (ew == 0 && lane == 0) {
@@ -1079,6 +1263,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int i = 0; i < ar_pending && !*abort_flag; ++i)
       if (!ar_reduce_tile(ar_tile[i])) break;
+    if (PAIR && lane == 0) bulk_wait_read_all();   // tile stores of this warp have finished reading its staging blocks
 #ifdef DPTB_GEMM_PROFILE
     if (ew == 0 && lane == 0) {
       DPTB_PROF_STORE(5, prof_wait_acc);
@@ -1091,10 +1276,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();   // neither CTA leaves while the other may still signal its barriers
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc<TMEM_COLS>(tmem_base);
+    if constexpr (PAIR) tmem_dealloc_pair<TMEM_COLS>(tmem_base);
+    else tmem_dealloc<TMEM_COLS>(tmem_base);
   }
   if (p.ar.world > 0 && threadIdx.x == 0) {
     // This rank's output is final once every rank has finished the tiles it owns.
@@ -1162,8 +1349,55 @@ static int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmP
   }
   const int tiles = p.tiles_m * p.tiles_n * p.splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, NoPeerMaps{}, p);
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, NoPeerMaps{}, EpiMaps{}, p);
   return counted(1, (int)cudaGetLastError());
+}
+
+// CTA-pair variant: clusters of two CTAs, one 256-row tile per pair (see the kernel's PAIR parameter).
+constexpr int kPairStages256 = 5;   // 32 KB per stage and CTA, 64 KB of epilogue staging
+constexpr int kPairStages128 = 6;   // 24 KB per stage and CTA
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+static int pair_clusters(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr) {
+  // Clusters of this kernel that can be resident at once (a persistent grid must not exceed it), once per process.
+  using L = GemmSmem<BN, STAGES, BN / 2, 2>;
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES, false, true>;
+  static int cached = -1;
+  if (cached < 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return 0;
+    cfg->gridDim = dim3(2 * (sm_count() / 2));
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cached = n;
+    if (getenv("DPTB_GEMM_VERBOSE")) fprintf(stderr, "gemm pair BN=%d: %d clusters of 2 CTAs can be resident\n", BN, n);
+  }
+  (void)attr;
+  return cached;
+}
+template <bool A_MN, bool B_MN, int BN, int STAGES>
+static int launch_tc_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const EpiMaps& em, const GemmParams& p,
+                          cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES, BN / 2, 2>;
+  auto kern = gemm_tc_kernel<A_MN, B_MN, BN, STAGES, false, true>;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const int max_clusters = pair_clusters<A_MN, B_MN, BN, STAGES>(&cfg, attr);
+  if (max_clusters <= 0) return kErrUnsupported;
+  const int units = ((p.tiles_m + 1) / 2) * p.tiles_n * p.splits;
+  const int clusters = units < max_clusters ? units : max_clusters;
+  cfg.gridDim = dim3(2 * clusters);
+  return counted(1, (int)cudaLaunchKernelEx(&cfg, kern, tmA, tmB, NoPeerMaps{}, em, p));
 }
 
 // All-gather variant: A (K-major) comes from every rank's shard, B is an nn.Linear weight (K-major).
@@ -1178,7 +1412,7 @@ static int launch_tc_ag(const TmapSet& peers, const CUtensorMap& tmB, const Gemm
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(peers.m[p.ag.rank], tmB, peers, p);
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(peers.m[p.ag.rank], tmB, peers, EpiMaps{}, p);
   return counted(1, (int)cudaGetLastError());
 }
 
@@ -1260,9 +1494,18 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
   //   a CTA runs ceil(units / SMs) units back to back; a unit costs its k-blocks (a 128-wide tile moves as many bytes
   //   for half the math, so its k-block counts 0.75) plus a fixed prologue/epilogue, plus the partial-tile round
   //   trip when K is split.
-  const int sms = sm_count();
   const int num_kb = (a->K + kBK - 1) / kBK;
   const int tm = (a->M + kBM - 1) / kBM;
+  // CTA pairs (256-row tiles shared by two SMs) for every plain GEMM with at least two row tiles; the fused
+  // tensor-parallel variants keep single CTAs.  DPTB_GEMM_PAIR=0 switches pairs off (for comparisons).
+  static const bool pairs_enabled = [] {
+    const char* e = getenv("DPTB_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  const bool pair = pairs_enabled && !ar && !ag && tm >= 2;
+  // Work units run on `sms` CTAs, or on sms / 2 pairs, each pair taking two row tiles at a time.
+  const int sms = pair ? sm_count() / 2 : sm_count();
+  const int tm_sched = pair ? (tm + 1) / 2 : tm;
   int bn = a->bn, splits = a->splits;
   {
     double best = 1e30;
@@ -1271,6 +1514,7 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
       if (a->bn == 128 || a->bn == 256) { if (cand_bn != a->bn) continue; }
       if (cand_bn == 256 && a->N <= 128) continue;
       const int tiles = tm * ((a->N + cand_bn - 1) / cand_bn);
+      const int sched_tiles = tm_sched * ((a->N + cand_bn - 1) / cand_bn);
       for (int sp = 1; sp <= 8; ++sp) {
         if (a->splits >= 1 && sp != a->splits) continue;
         if ((ar || ag) && sp > 1) break;
@@ -1280,7 +1524,7 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
           if (num_kb / sp < 4) break;
         }
         const int kbs = (num_kb + sp - 1) / sp;
-        const long long units = (long long)tiles * sp;
+        const long long units = (long long)sched_tiles * sp;
         const double waves = (double)((units + sms - 1) / sms);
         const double per_kb = cand_bn == 256 ? 1.0 : 0.75;
         const double fixed = (cand_bn == 256 ? 8.0 : 5.0) + (sp > 1 ? (cand_bn == 256 ? 6.0 + 1.5 * sp : 4.0 + 1.0 * sp) : 0.0);
@@ -1347,7 +1591,8 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
   if (a->trans_a) rc = encode_tmap_2d_bf16(&tmA, a->A, (uint64_t)a->M, (uint64_t)a->K, (uint64_t)a->lda * 2, 64, 64);
   else            rc = encode_tmap_2d_bf16(&tmA, a->A, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->lda * 2, 64, kBM);
   if (rc) return rc;
-  if (a->trans_b) rc = encode_tmap_2d_bf16(&tmB, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb * 2, 64, (uint32_t)bn);
+  if (a->trans_b) rc = encode_tmap_2d_bf16(&tmB, a->B, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->ldb * 2, 64,
+                                           (uint32_t)(pair ? bn / 2 : bn));
   else            rc = encode_tmap_2d_bf16(&tmB, a->B, (uint64_t)a->N, (uint64_t)a->K, (uint64_t)a->ldb * 2, 64, 64);
   if (rc) return rc;
 
@@ -1365,9 +1610,32 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
       p.row_epi = 2;
   }
 
+  // CTA pairs with a bf16 output take the tile-store epilogue when every per-element buffer can be described by a
+  // tensor map (16-byte aligned, row strides multiples of 16 bytes: vec_ok), at most one per-element input is read
+  // and a pre-activation copy is not combined with an input (the two staging blocks of a warp cover either case).
+  EpiMaps em;
+  if (pair && p.row_epi && p.splits == 1 && (a->N % 8) == 0) {
+    const int inputs = (p.act >= 11 ? 1 : 0) + (p.residual ? 1 : 0) + (p.accumulate ? 1 : 0);
+    if (inputs <= 1 && !(inputs == 1 && p.aux_out)) {
+      const void* in_ptr = p.act >= 11 ? (const void*)p.aux_in : (p.residual ? (const void*)p.residual : p.C);
+      const long long in_ld = p.act >= 11 ? p.ld_aux_in : (p.residual ? p.ldr : p.ldc);
+      int e = encode_tmap_2d_bf16(&em.c, p.C, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)p.ldc * 2, 64, 32);
+      if (!e) e = p.aux_out ? encode_tmap_2d_bf16(&em.aux, p.aux_out, (uint64_t)a->N, (uint64_t)a->M,
+                                                  (uint64_t)p.ld_aux_out * 2, 64, 32)
+                            : (em.aux = em.c, 0);
+      if (!e) e = inputs ? encode_tmap_2d_bf16(&em.in, in_ptr, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)in_ld * 2, 64, 32)
+                         : (em.in = em.c, 0);
+      if (e) return e;
+      p.row_epi = 3;
+    }
+  }
+  if (p.row_epi != 3) em.c = em.aux = em.in = tmA;   // unused by the kernel, but kernel parameters must be initialised
+
   const bool amn = a->trans_a != 0, bmn = a->trans_b == 0;
-#define DPTB_LAUNCH(AMN, BMN)                                                        \
-  (bn == 256 ? launch_tc<AMN, BMN, 256, 4>(tmA, tmB, p, stream) : launch_tc<AMN, BMN, 128, 6>(tmA, tmB, p, stream))
+#define DPTB_LAUNCH(AMN, BMN)                                                                                         \
+  (pair ? (bn == 256 ? launch_tc_pair<AMN, BMN, 256, kPairStages256>(tmA, tmB, em, p, stream)                          \
+                     : launch_tc_pair<AMN, BMN, 128, kPairStages128>(tmA, tmB, em, p, stream))                         \
+        : (bn == 256 ? launch_tc<AMN, BMN, 256, 4>(tmA, tmB, p, stream) : launch_tc<AMN, BMN, 128, 6>(tmA, tmB, p, stream)))
   if (!amn && !bmn) return DPTB_LAUNCH(false, false);
   if (!amn && bmn) return DPTB_LAUNCH(false, true);
   if (amn && !bmn) return DPTB_LAUNCH(true, false);

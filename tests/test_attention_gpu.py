@@ -34,9 +34,9 @@ FWD_CASES = [
     (1, 128, 1, 1, 64, False), (1, 128, 1, 1, 64, True), (2, 256, 2, 2, 64, True), (2, 384, 3, 3, 64, True),
     (2, 1024, 4, 4, 64, True), (3, 197, 2, 2, 64, False), (1, 300, 2, 1, 64, True), (2, 512, 4, 2, 64, False),
     (1, 128, 1, 1, 128, True), (2, 256, 4, 1, 128, True), (1, 1000, 2, 2, 128, False),
-    # head sizes the kernels take zero-padded to 64 / 128
-    (2, 200, 4, 4, 32, True), (1, 96, 2, 1, 16, True), (2, 64, 2, 2, 8, False), (1, 256, 2, 2, 96, True),
 ]
+# head sizes the kernels take zero-padded to 64 / 128 (through the public wrapper, which does the padding)
+PADDED_FWD_CASES = [(2, 200, 4, 4, 32, True), (1, 96, 2, 1, 16, True), (2, 64, 2, 2, 8, False), (1, 256, 2, 2, 96, True)]
 
 
 @pytest.mark.parametrize("B,S,H,Hkv,hd,causal", FWD_CASES)
@@ -53,6 +53,18 @@ def test_attention_forward(B, S, H, Hkv, hd, causal):
     if causal:
         s = s + torch.triu(torch.full((S, S), float("-inf"), device="cuda"), 1)
     assert _rel(lse, torch.logsumexp(s, -1)) < 1e-3
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,hd,causal", PADDED_FWD_CASES)
+def test_attention_forward_padded_head_sizes(B, S, H, Hkv, hd, causal):
+    qkv = _qkv(B, S, H, Hkv, hd)
+    before = _launches()
+    o = A.attention_packed(qkv, B, S, H, Hkv, hd, causal)
+    assert _launches() - before == 1            # one flash kernel, not a GEMM + softmax per (batch, head)
+    q, k, v = _split(qkv, B, S, H, Hkv, hd)
+    ref = R.attention(q, k, v, causal=causal).transpose(1, 2).reshape(B * S, H * hd)
+    assert o.shape == ref.shape and torch.isfinite(o.float()).all()
+    assert _rel(o, ref) < 2e-2
 
 
 def test_attention_forward_q_offset():
