@@ -68,20 +68,31 @@ def build_cases(dev, want=()):
             nbytes += 2 * m * n
         if kw.get("act"):
             extra["act"] = kw["act"]
+        if kw.get("aux_out"):          # pre-activation copy kept for the backward pass
+            extra["aux_out"] = torch.empty(m, n, **bf)
+            nbytes += 2 * m * n
+        if kw.get("act_bwd"):          # multiply by act'(pre-activation) in the epilogue
+            extra["aux_in"] = torch.randn(m, n, **bf)
+            extra["act_bwd"] = kw["act_bwd"]
+            nbytes += 2 * m * n
+        if kw.get("accumulate"):       # weight gradients add into the flat gradient buffer
+            extra["accumulate"] = True
+            c.zero_()
+            nbytes += 2 * m * n
         cases[name] = (lambda: K.gemm(a, b, c, trans_a=ta, trans_b=tb, **extra), nbytes, 2.0 * m * n * k)
 
     gemm_case("gemm_qkv_fwd", M, 3 * D, D, False, True, bias=True)
     gemm_case("gemm_proj_fwd", M, D, D, False, True, bias=True, residual=True)
-    gemm_case("gemm_fc1_fwd_gelu", M, 4 * D, D, False, True, bias=True, act="gelu_tanh")
+    gemm_case("gemm_fc1_fwd_gelu", M, 4 * D, D, False, True, bias=True, act="gelu_tanh", aux_out=True)
     gemm_case("gemm_fc2_fwd", M, D, 4 * D, False, True, bias=True, residual=True)
     gemm_case("gemm_lmhead_fwd", M, VP, D, False, True)
     gemm_case("gemm_fc1_dgrad", M, D, 4 * D, False, False)
-    gemm_case("gemm_fc2_dgrad", M, 4 * D, D, False, False)
+    gemm_case("gemm_fc2_dgrad", M, 4 * D, D, False, False, act_bwd="gelu_tanh")
     gemm_case("gemm_qkv_dgrad", M, D, 3 * D, False, False)
-    gemm_case("gemm_fc1_wgrad", 4 * D, D, M, True, False)
-    gemm_case("gemm_fc2_wgrad", D, 4 * D, M, True, False)
-    gemm_case("gemm_qkv_wgrad", 3 * D, D, M, True, False)
-    gemm_case("gemm_proj_wgrad", D, D, M, True, False)
+    gemm_case("gemm_fc1_wgrad", 4 * D, D, M, True, False, accumulate=True)
+    gemm_case("gemm_fc2_wgrad", D, 4 * D, M, True, False, accumulate=True)
+    gemm_case("gemm_qkv_wgrad", 3 * D, D, M, True, False, accumulate=True)
+    gemm_case("gemm_proj_wgrad", D, D, M, True, False, accumulate=True)
     gemm_case("gemm_8192", 8192, 8192, 8192, False, True)
     # decode-sized rows: the per-GPU projections of a Llama-3-8B layer at TP = 8, batch 32 (weight streaming)
     gemm_case("gemm_dec_qkv", 32, 768, 4096, False, True)

@@ -474,14 +474,9 @@ __device__ __forceinline__ void epi_prefetch(const GemmParams& p, uint32_t* bias
   }
   if (p.bias) bias_s[lane] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col0) + lane);
 }
-// TMA = true: outputs leave through shared memory and one tile store per block (`buf_aux` / `buf_c`: 4 KB staging
-// blocks of this warp, `em`: the tensor maps); the caller has made `buf_aux` free, and this function frees `buf_c`
-// (waits for the store that last read it) before writing it.  Rows and columns outside the matrix are clipped by the copy.
-template <bool TMA = false>
 __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32_t* bias_s, long long row0,
                                                long long col0, int lane, const uint32_t (&r0)[32],
-                                               const uint32_t (&r1)[32], const EpiIn& in, uint8_t* buf_aux = nullptr,
-                                               uint8_t* buf_c = nullptr, const EpiMaps* em = nullptr) {
+                                               const uint32_t (&r1)[32], const EpiIn& in) {
   const long long row = row0 + lane;
   const bool live = row < p.M;
   const bool wide = p.row_epi == 2;
@@ -507,19 +502,7 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
     uint4 o[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
-    if constexpr (TMA) {
-      st_smem_row64(buf_aux, lane, o);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_2d(&em->aux, buf_aux, (int)col0, (int)row0);
-        bulk_commit_group();
-        bulk_wait_read_1();     // the store before this one (which read buf_c) has finished reading
-      }
-      __syncwarp();
-    } else {
-      if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
-    }
+    if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
   }
   if (p.act == 2) {
     // GELU (tanh form), the one activation on the training hot path, outside the per-group dispatch: five
@@ -583,17 +566,78 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
   uint4 o[8];
 #pragma unroll
   for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
-  if constexpr (TMA) {
-    st_smem_row64(buf_c, lane, o);
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(&em->c, buf_c, (int)col0, (int)row0);
-      bulk_commit_group();
-    }
-  } else {
-    if (live) st_row64(static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0, wide, o);
+  if (live) st_row64(static_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0, wide, o);
+}
+
+// Tile-store epilogue, one half (32 columns) of a thread's row at a time so that the values, the per-element input and
+// the packed output of a half fit in registers together.  `r` holds the accumulators of columns [32 h, 32 h + 32) of the
+// 64-column block; the input (if any) is read from, and the output written to, chunks 4 h .. 4 h + 3 of the thread's
+// row in the swizzled staging blocks.  bias -> (copy to buf_aux) -> activation -> activation' -> + input -> buf_c.
+__device__ __forceinline__ void epi_half_tma(const GemmParams& p, const uint32_t* bias_s, int h, int lane, int in_kind,
+                                             const uint32_t (&r)[32], uint8_t* buf_aux, uint8_t* buf_c) {
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  if (p.alpha != 1.0f) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
   }
+  if (p.bias) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(bias_s + (h * 4 + g) * 4), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[g * 8 + e] += f[e];
+    }
+  }
+  uint8_t* row_aux = buf_aux + lane * 128;
+  uint8_t* row_c = buf_c + lane * 128;
+  if (p.aux_out) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      *reinterpret_cast<uint4*>(row_aux + (((h * 4 + g) ^ (lane & 7)) << 4)) =
+          pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
+  }
+  if (p.act == 2) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float x = v[i];
+      const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);
+      const float hx = 0.5f * x;
+      v[i] = fmaf(hx, tanh_fast(u), hx);
+    }
+  } else if (p.act >= 1 && p.act <= 4) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) apply_act8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]));
+  }
+  if (in_kind) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float x[8];
+      unpack8(*reinterpret_cast<const uint4*>(row_c + (((h * 4 + g) ^ (lane & 7)) << 4)), x);
+      if (in_kind == 1) {
+        if (p.act == 12) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float xx = x[e] * x[e];
+            const float t = tanh_fast(x[e] * fmaf(xx, 0.0356774081f, 0.7978845608f));
+            const float sl = x[e] * fmaf(xx, 0.1070322243f, 0.7978845608f);
+            v[g * 8 + e] *= 0.5f * (1.0f + t + sl * fmaf(-t, t, 1.0f));
+          }
+        } else {
+          apply_act_bwd8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]), x);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[g * 8 + e] += x[e];
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+    *reinterpret_cast<uint4*>(row_c + (((h * 4 + g) ^ (lane & 7)) << 4)) =
+        pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
 }
 
 // ----------------------------------------------------------------------------- all-reduce epilogue helpers
@@ -1052,14 +1096,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       // Tile-store epilogue: this warp's bias slices are requested before the wait for the accumulator.
+      // and the per-element input blocks (residual / activation input / C) are fetched into the staging blocks by tile
+      // loads, so that neither latency is paid after the accumulator has arrived.
       uint32_t bias_pf[BN / 128] = {};
+      const int epi_in_kind = p.act >= 11 ? 1 : (p.residual ? 2 : (p.accumulate ? 3 : 0));
       if constexpr (PAIR) {
-        if (p.row_epi == 3 && p.bias && mi < p.tiles_m) {
+        if (p.row_epi == 3 && p.splits == 1 && mi < p.tiles_m && (long long)m0 + q * 32 < p.M) {
+          if (p.bias) {
 #pragma unroll
-          for (int j = 0; j < BN / 128; ++j) {
-            const long long col = (long long)n0 + (half + 2 * j) * 64 + 2 * lane;
-            if (col < p.N)
-              bias_pf[j] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col));
+            for (int j = 0; j < BN / 128; ++j) {
+              const long long col = (long long)n0 + (half + 2 * j) * 64 + 2 * lane;
+              if (col < p.N)
+                bias_pf[j] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col));
+            }
+          }
+          if (epi_in_kind && lane == 0) {
+            int nblk = 0;
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) nblk += ((long long)n0 + (half + 2 * j) * 64 < p.N) ? 1 : 0;
+            if (nblk > 0) {
+              bulk_wait_read_all();   // the previous tile's stores have finished reading both staging blocks
+              mbar_arrive_expect_tx(&epi_in_bar[ew], 4096u * nblk);
+              for (int j = 0; j < nblk; ++j)
+                tma_load_2d(stage + j * 4096, &em.in, &epi_in_bar[ew], n0 + (half + 2 * j) * 64, m0 + q * 32);
+            }
           }
         }
       }
@@ -1075,7 +1135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       const long long row0 = (long long)m0 + q * 32;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      if (p.ar.world > 0) {
+      if (!PAIR && p.ar.world > 0) {
         // Partial tile -> this rank's partial buffer (each thread writes its row's 128 bytes of a 64-column block as
         // whole sectors); flag the owner.  The CTA-wide barrier orders every warp's stores before the one
         // release-at-system-scope store of the flag (release is cumulative over that synchronisation).
@@ -1116,10 +1176,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           ar_tile[ar_pending++] = tile;
         }
-      } else if (PAIR && p.splits == 1 && p.row_epi == 3) {
+      } else if (PAIR && p.splits == 1) {   // pairs are launched only for outputs this epilogue can take
         // Tile-store epilogue: registers -> swizzled staging block -> one tile store per 32 x 64 block, with the
         // per-element input (if any) fetched into the same block by a tile load while the accumulator is read.
-        const int in_kind = p.act >= 11 ? 1 : (p.residual ? 2 : (p.accumulate ? 3 : 0));
+        const int in_kind = epi_in_kind;
         const bool rows_live = row0 < p.M;   // warp-uniform
         bool ok = true;
 #pragma unroll 1
@@ -1127,33 +1187,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int c = half + 2 * j;
           const long long col0 = (long long)n0 + c * 64;
           if (col0 >= p.N || !rows_live) break;  // warp-uniform
+          // Staging block of the output: with an input, the block the input of this chunk was loaded into; with a
+          // pre-activation copy, block 1 (block 0 stages the copy); else the two blocks alternate.
           uint8_t* buf_aux = stage;
-          uint8_t* buf_c = stage + (p.aux_out ? 4096 : (int)(epi_blk & 1) * 4096);
+          uint8_t* buf_c = stage + (in_kind ? j * 4096 : (p.aux_out ? 4096 : (int)(epi_blk & 1) * 4096));
           DPTB_PROF_BEGIN(prof_c0);
-          if (lane == 0) {
-            bulk_wait_read_1();   // the store that last read the block about to be overwritten has finished reading
-            if (in_kind) {
-              mbar_arrive_expect_tx(&epi_in_bar[ew], 4096);
-              tma_load_2d(buf_c, &em.in, &epi_in_bar[ew], (int)col0, (int)row0);
-            }
-          }
-          __syncwarp();
           uint32_t r0[32], r1[32];
           tmem_ld_32x32(t_row + c * 64, r0);
           tmem_ld_32x32(t_row + c * 64 + 32, r1);
           if (p.bias) bias_s[lane] = bias_pf[j];
-          EpiIn in;
-          in.kind = in_kind;
-          tmem_ld_wait();
-          if (in_kind) {
+          if (!in_kind && lane == 0) {
+            // the stores that last read the block(s) about to be overwritten have finished reading
+            if (p.aux_out) bulk_wait_read_all();
+            else bulk_wait_read_1();
+          }
+          if (in_kind && j == 0) {   // one barrier phase per tile covers both input blocks
             ok = __all_sync(0xffffffffu, mbar_wait(&epi_in_bar[ew], epi_in_ph, abort_flag, kWaitFullTimeout));
             epi_in_ph ^= 1;
-            if (!ok) break;
-            ld_smem_row64(buf_c, lane, in.v);
           }
+          tmem_ld_wait();
+          __syncwarp();              // bias slice and buffer release are visible to every lane
+          if (!ok) break;
           DPTB_PROF_END(prof_c0, prof_ld);
           DPTB_PROF_BEGIN(prof_c1);
-          epi_finish_row<true>(p, bias_s, row0, col0, lane, r0, r1, in, buf_aux, buf_c, &em);
+          epi_half_tma(p, bias_s, 0, lane, in_kind, r0, buf_aux, buf_c);
+          epi_half_tma(p, bias_s, 1, lane, in_kind, r1, buf_aux, buf_c);
+          fence_proxy_async_smem();
+          __syncwarp();              // also: every lane has read the bias slice before the next block rewrites it
+          if (lane == 0) {
+            if (p.aux_out) {
+              tma_store_2d(&em.aux, buf_aux, (int)col0, (int)row0);
+              bulk_commit_group();
+            }
+            tma_store_2d(&em.c, buf_c, (int)col0, (int)row0);
+            bulk_commit_group();
+          }
           DPTB_PROF_END(prof_c1, prof_fin);
           ++epi_blk;
 #ifdef DPTB_GEMM_PROFILE
@@ -1164,7 +1232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) release_acc(acc);
-      } else if (p.splits == 1) {
+      } else if (!PAIR && p.splits == 1) {
 #pragma unroll 1
         for (int c = half; c < BN / 64; c += 2) {
           const long long col0 = (long long)n0 + c * 64;
@@ -1261,8 +1329,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!epi_sync()) break;  // epi_last may be rewritten only after every warp has read it
       }
     }
-    for (int i = 0; i < ar_pending && !*abort_flag; ++i)
-      if (!ar_reduce_tile(ar_tile[i])) break;
+    if constexpr (!PAIR) {
+      for (int i = 0; i < ar_pending && !*abort_flag; ++i)
+        if (!ar_reduce_tile(ar_tile[i])) break;
+    }
     if (PAIR && lane == 0) bulk_wait_read_all();   // tile stores of this warp have finished reading its staging blocks
 #ifdef DPTB_GEMM_PROFILE
     if (ew == 0 && lane == 0) {
@@ -1283,7 +1353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if constexpr (PAIR) tmem_dealloc_pair<TMEM_COLS>(tmem_base);
     else tmem_dealloc<TMEM_COLS>(tmem_base);
   }
-  if (p.ar.world > 0 && threadIdx.x == 0) {
+  if (!PAIR && p.ar.world > 0 && threadIdx.x == 0) {
     // This rank's output is final once every rank has finished the tiles it owns.
     __threadfence_system();
     if (atomicAdd(p.ar.exit_counter, 1u) == gridDim.x - 1) {
@@ -1502,7 +1572,13 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
     const char* e = getenv("DPTB_GEMM_PAIR");
     return !(e && e[0] == '0');
   }();
-  const bool pair = pairs_enabled && !ar && !ag && tm >= 2;
+  // A pair's epilogue leaves through tile stores: bf16 output, every per-element buffer describable by a tensor map
+  // (16-byte aligned, strides multiples of 16 bytes), at most one per-element input, and a pre-activation copy not
+  // combined with an input (a warp's two staging blocks cover either case).
+  const int epi_inputs = (p.act >= 11 ? 1 : 0) + (p.residual ? 1 : 0) + (p.accumulate ? 1 : 0);
+  const bool tile_store_ok = !p.out_f32 && p.vec_ok && !(p.bias && p.bias_f32) && (a->N % 8) == 0 && epi_inputs <= 1 &&
+                             !(epi_inputs == 1 && p.aux_out);
+  const bool pair = pairs_enabled && !ar && !ag && tm >= 2 && tile_store_ok;
   // Work units run on `sms` CTAs, or on sms / 2 pairs, each pair taking two row tiles at a time.
   const int sms = pair ? sm_count() / 2 : sm_count();
   const int tm_sched = pair ? (tm + 1) / 2 : tm;
@@ -1614,9 +1690,9 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
   // tensor map (16-byte aligned, row strides multiples of 16 bytes: vec_ok), at most one per-element input is read
   // and a pre-activation copy is not combined with an input (the two staging blocks of a warp cover either case).
   EpiMaps em;
-  if (pair && p.row_epi && p.splits == 1 && (a->N % 8) == 0) {
-    const int inputs = (p.act >= 11 ? 1 : 0) + (p.residual ? 1 : 0) + (p.accumulate ? 1 : 0);
-    if (inputs <= 1 && !(inputs == 1 && p.aux_out)) {
+  if (pair && p.splits == 1) {
+    const int inputs = epi_inputs;
+    {
       const void* in_ptr = p.act >= 11 ? (const void*)p.aux_in : (p.residual ? (const void*)p.residual : p.C);
       const long long in_ld = p.act >= 11 ? p.ld_aux_in : (p.residual ? p.ldr : p.ldc);
       int e = encode_tmap_2d_bf16(&em.c, p.C, (uint64_t)a->N, (uint64_t)a->M, (uint64_t)p.ldc * 2, 64, 32);
