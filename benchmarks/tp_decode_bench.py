@@ -104,6 +104,169 @@ class TorchTPLlama:
         best = torch.stack(vals).argmax(0)
         return torch.stack(idxs).gather(0, best[None])[0]
 
+    @torch.no_grad()
+    def decode_static(self, tok, pos):
+        """One decode step with static shapes, so that it can be captured in a CUDA graph: the position is a device
+        tensor, the new K / V rows are written with ``index_copy_`` and attention runs over the whole cache under a
+        length mask.  ``tok [B]`` and ``pos [1]`` (int64) are updated in place."""
+        import torch.nn.functional as Fn
+        c, hd = self.c, self.c.head_dim
+        B = tok.shape[0]
+        max_ctx = self.layers[0]["k"].shape[2]
+        x = self.embed[tok].view(B, 1, -1)
+        cs, sn = self.cos.index_select(0, pos).view(1, 1, 1, -1), self.sin.index_select(0, pos).view(1, 1, 1, -1)
+        mask = (torch.arange(max_ctx, device=tok.device) <= pos).view(1, 1, 1, max_ctx)
+
+        def rope(t):
+            half = t.shape[-1] // 2
+            a, b = t[..., :half].float(), t[..., half:].float()
+            return torch.cat([a * cs - b * sn, b * cs + a * sn], -1).to(t.dtype)
+        for L in self.layers:
+            y = Fn.rms_norm(x, (c.embed_dim,), L["n1"], c.rms_norm_eps)
+            qkv = y @ L["qkv"].t()
+            q, k, v = qkv.split([self.Hq * hd, self.Hkv * hd, self.Hkv * hd], -1)
+            q = rope(q.view(B, 1, self.Hq, hd).transpose(1, 2))
+            k = rope(k.view(B, 1, self.Hkv, hd).transpose(1, 2))
+            v = v.view(B, 1, self.Hkv, hd).transpose(1, 2)
+            L["k"][:B].index_copy_(2, pos, k)
+            L["v"][:B].index_copy_(2, pos, v)
+            qg = q.reshape(B, self.Hkv, self.Hq // self.Hkv, hd)
+            o = Fn.scaled_dot_product_attention(qg, L["k"][:B], L["v"][:B], attn_mask=mask).reshape(B, 1, self.Hq * hd)
+            part = o @ L["wo"].t()
+            dist.all_reduce(part, group=self.group)
+            x = x + part
+            y = Fn.rms_norm(x, (c.embed_dim,), L["n2"], c.rms_norm_eps)
+            gu = y @ L["gu"].t()
+            h = Fn.silu(gu[..., :self.F]) * gu[..., self.F:]
+            part = h @ L["down"].t()
+            dist.all_reduce(part, group=self.group)
+            x = x + part
+        xf = Fn.rms_norm(x[:, -1], (c.embed_dim,), self.nf, c.rms_norm_eps)
+        logits = xf @ self.head.t()
+        val, idx = logits.float().max(-1)
+        vals = torch.empty(self.T, B, device=tok.device)
+        idxs = torch.empty(self.T, B, dtype=torch.long, device=tok.device)
+        dist.all_gather_into_tensor(vals, val, group=self.group)
+        dist.all_gather_into_tensor(idxs, idx + self.rank * self.Vl, group=self.group)
+        tok.copy_(idxs.gather(0, vals.argmax(0)[None])[0])
+        pos.add_(1)
+
+
+def measure(impl: str, layers: int, B: int, S: int, NEW: int, prefill_rows: int = 65536, prefill_reps: int = 3,
+            use_graph: bool = True, group=None, prefill_modes=("ar",)):
+    """Prefill (TTFT) and greedy-decode throughput of the Llama-3-8B-shaped model on the ranks of ``group``
+    (``torch.distributed`` must be initialised).  Returns the result dict on every rank (times are the max over
+    ranks).  ``prefill_modes``: which prefill schedules of ``TPLlamaEngine`` to time ("ar": replicated activations,
+    GEMM + all-reduce; "sp": row-sharded activations, GEMM + reduce-scatter / all-gather + GEMM); the fastest is the
+    reported TTFT."""
+    group = group if group is not None else dist.group.WORLD
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    max_ctx = S + NEW
+    cfg = llama8b_config(layers, max_ctx)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab_size, (B, S), generator=g).cuda()
+    chunk = max(1, prefill_rows // S)
+    note = {}
+    if impl == "ours":
+        from dart_pytorch_b200 import _native
+        from dart_pytorch_b200.parallel.tp_llama import TPLlamaEngine
+        eng = TPLlamaEngine(cfg, max_batch=B, max_ctx=max_ctx, max_rows=max(prefill_rows, B), group=group)
+
+        def prefill(mode="ar"):
+            eng.reset()
+            return eng.prefill(prompts, chunk=chunk, mode=mode)
+
+        def step():
+            return eng.decode_step(B, use_graph=use_graph)
+        note["cuda_graph_decode"] = bool(use_graph)
+    else:
+        eng = TorchTPLlama(cfg, B, max_ctx, group)
+        state = {"tok": None, "pos": 0, "graph": None}
+        stok = torch.zeros(B, dtype=torch.long, device="cuda")
+        spos = torch.zeros(1, dtype=torch.long, device="cuda")
+
+        def prefill(mode="ar"):
+            outs = [eng.forward(prompts[b0:b0 + chunk], 0, b0) for b0 in range(0, B, chunk)]
+            state["tok"], state["pos"] = torch.cat(outs), S
+            stok.copy_(state["tok"])
+            spos.fill_(S)
+            return state["tok"]
+
+        def capture():
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            saved = (stok.clone(), spos.clone())
+            try:
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        eng.decode_static(stok, spos)
+                    torch.cuda.synchronize()
+                    dist.barrier(group=group)
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr, stream=side):
+                        eng.decode_static(stok, spos)
+                state["graph"] = gr
+                note["cuda_graph_decode"] = True
+            except Exception as e:      # keep the eager step and say why
+                torch.cuda.synchronize()
+                note["cuda_graph_decode"] = False
+                note["graph_error"] = repr(e)[:160]
+            torch.cuda.current_stream().wait_stream(side)
+            stok.copy_(saved[0])
+            spos.copy_(saved[1])
+
+        def step():
+            if state["graph"] is not None:
+                state["graph"].replay()
+                return stok
+            state["tok"] = eng.forward(state["tok"].view(B, 1), state["pos"])
+            state["pos"] += 1
+            return state["tok"]
+        prefill_modes = ("ar",)
+
+    def timed(fn):
+        dist.barrier(group=group)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t.item())
+
+    ttft = {}
+    for mode in prefill_modes:
+        prefill(mode)                                     # warm-up (allocations, descriptor caches)
+        ttft[mode] = sorted(timed(lambda: prefill(mode)) for _ in range(prefill_reps))
+    best_mode = min(ttft, key=lambda m: ttft[m][len(ttft[m]) // 2])
+    prefill(best_mode)
+    if impl == "torch" and use_graph:
+        capture()
+    for _ in range(3):                                    # decode warm-up; builds the CUDA graph for `ours`
+        step()
+    steps = NEW - 4
+
+    def run_decode():
+        for _ in range(steps):
+            step()
+    ms = timed(run_decode)
+    if impl == "ours":
+        _native.raise_on_device_error()
+    med = {m: v[len(v) // 2] for m, v in ttft.items()}
+    out = {"metric": "llama8b_tp_decode_tokens_per_s", "value": B * steps / (ms / 1e3), "unit": "tokens/s",
+           "impl": impl, "n_gpus": world, "ttft_ms_p50": med[best_mode], "ttft_ms_all": ttft[best_mode],
+           "ttft_ms_p50_by_prefill_mode": med, "prefill_mode": best_mode,
+           "decode_ms_per_step": ms / steps, "decode_steps": steps, "dtype": "bf16", "data": "synthetic",
+           "config": dict({"model": f"llama-3-8b-shaped ({layers} layers)", "batch": B, "prompt": S, "new": NEW,
+                           "parallelism": f"tp{world}", "prefill_rows_per_call": prefill_rows}, **note)}
+    if impl == "ours":
+        out["nvls"] = bool(eng.comm.use_nvls)
+    del eng
+    torch.cuda.empty_cache()
+    return out
+
 
 def main():
     ap = argparse.ArgumentParser()
@@ -115,81 +278,15 @@ def main():
     ap.add_argument("--prefill-rows", type=int, default=65536,
                     help="token rows per prefill call (whole sequences); both implementations use the same chunking")
     ap.add_argument("--prefill-reps", type=int, default=3)
+    ap.add_argument("--prefill-modes", default="ar,sp")
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
-    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    rank, local = int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    group = dist.group.WORLD
-    B, S, NEW = args.batch, args.prompt, args.new
-    max_ctx = S + NEW
-    cfg = llama8b_config(args.layers, max_ctx)
-    g = torch.Generator().manual_seed(0)
-    prompts = torch.randint(0, cfg.vocab_size, (B, S), generator=g).cuda()
-    launches = 0
-    if args.impl == "ours":
-        from dart_pytorch_b200 import _native
-        from dart_pytorch_b200.parallel.tp_llama import TPLlamaEngine
-        eng = TPLlamaEngine(cfg, max_batch=B, max_ctx=max_ctx, max_rows=max(args.prefill_rows, B))
-        chunk = max(1, args.prefill_rows // S)
-
-        def prefill():
-            eng.reset()
-            return eng.prefill(prompts, chunk=chunk)
-
-        def step():
-            return eng.decode_step(B, use_graph=not args.no_graph)
-    else:
-        eng = TorchTPLlama(cfg, B, max_ctx, group)
-        chunk = max(1, args.prefill_rows // S)
-        state = {"tok": None, "pos": 0}
-
-        def prefill():
-            outs = [eng.forward(prompts[b0:b0 + chunk], 0, b0) for b0 in range(0, B, chunk)]
-            state["tok"], state["pos"] = torch.cat(outs), S
-            return state["tok"]
-
-        def step():
-            state["tok"] = eng.forward(state["tok"].view(B, 1), state["pos"])
-            state["pos"] += 1
-            return state["tok"]
-
-    def timed(fn):
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    prefill()                                             # warm-up (allocations, descriptor caches)
-    ttft = sorted(timed(prefill) for _ in range(args.prefill_reps))
-    for _ in range(3):                                    # decode warm-up; builds the CUDA graph for `ours`
-        step()
-    if args.impl == "ours":
-        _native.launch_count_reset() if hasattr(_native, "launch_count_reset") else None
-    steps = NEW - 4
-
-    def run_decode():
-        for _ in range(steps):
-            step()
-    ms = timed(run_decode)
-    if args.impl == "ours":
-        from dart_pytorch_b200 import _native as N_
-        N_.raise_on_device_error()
+    out = measure(args.impl, args.layers, args.batch, args.prompt, args.new, args.prefill_rows, args.prefill_reps,
+                  use_graph=not args.no_graph, prefill_modes=tuple(m for m in args.prefill_modes.split(",") if m))
     if rank == 0:
-        out = {"metric": "llama8b_tp_decode_tokens_per_s", "value": B * steps / (ms / 1e3), "unit": "tokens/s",
-               "impl": args.impl, "n_gpus": world, "ttft_ms_p50": ttft[len(ttft) // 2], "ttft_ms_all": ttft,
-               "decode_ms_per_step": ms / steps, "decode_steps": steps, "dtype": "bf16", "data": "synthetic",
-               "config": {"model": f"llama-3-8b-shaped ({args.layers} layers)", "batch": B, "prompt": S, "new": NEW,
-                          "parallelism": f"tp{world}", "prefill_rows_per_call": args.prefill_rows,
-                          "cuda_graph_decode": args.impl == "ours" and not args.no_graph}}
-        if args.impl == "ours":
-            out["nvls"] = bool(eng.comm.use_nvls)
         print(json.dumps(out))
     dist.barrier()
     dist.destroy_process_group()

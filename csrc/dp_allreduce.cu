@@ -76,35 +76,51 @@ dp_allreduce_kernel(const DpArgs a) {
     const long long v0 = per * a.rank;
     const long long v1 = v0 + per < nvec ? v0 + per : nvec;
     const float inv = 1.0f / (float)a.world;
-    for (long long v = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v1;
-         v += (long long)gridDim.x * blockDim.x) {
-      const long long off = a.start + v * 8;
-      float f[8];
-      if (NVLS) {
-        const uint4 u = multimem_ld_reduce_bf16x8(a.mc_base + off);
-        const float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y), p2 = unpack_bf16x2(u.z), p3 = unpack_bf16x2(u.w);
-        f[0] = p0.x; f[1] = p0.y; f[2] = p1.x; f[3] = p1.y; f[4] = p2.x; f[5] = p2.y; f[6] = p3.x; f[7] = p3.y;
-      } else {
+    // Four 16-byte vectors per thread and iteration: all four remote loads are issued before the first is used, so
+    // a thread keeps 64 bytes in flight across the NVLink round trip instead of 16.
+    constexpr int kUnroll = 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long vb = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; vb < v1; vb += stride * kUnroll) {
+      float f[kUnroll][8];
+      bool live[kUnroll];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = 0.0f;
-        for (int r = 0; r < a.world; ++r) {
-          const uint4 u = ld_cg_v4(a.bases[r] + off);
-          const float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y), p2 = unpack_bf16x2(u.z), p3 = unpack_bf16x2(u.w);
-          f[0] += p0.x; f[1] += p0.y; f[2] += p1.x; f[3] += p1.y; f[4] += p2.x; f[5] += p2.y; f[6] += p3.x; f[7] += p3.y;
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long v = vb + u * stride;
+        live[u] = v < v1;
+        const long long off = a.start + (live[u] ? v : vb) * 8;
+        if (NVLS) {
+          const uint4 q = multimem_ld_reduce_bf16x8(a.mc_base + off);
+          const float2 p0 = unpack_bf16x2(q.x), p1 = unpack_bf16x2(q.y), p2 = unpack_bf16x2(q.z), p3 = unpack_bf16x2(q.w);
+          f[u][0] = p0.x; f[u][1] = p0.y; f[u][2] = p1.x; f[u][3] = p1.y;
+          f[u][4] = p2.x; f[u][5] = p2.y; f[u][6] = p3.x; f[u][7] = p3.y;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[u][i] = 0.0f;
+          for (int r = 0; r < a.world; ++r) {
+            const uint4 q = ld_cg_v4(a.bases[r] + off);
+            const float2 p0 = unpack_bf16x2(q.x), p1 = unpack_bf16x2(q.y), p2 = unpack_bf16x2(q.z), p3 = unpack_bf16x2(q.w);
+            f[u][0] += p0.x; f[u][1] += p0.y; f[u][2] += p1.x; f[u][3] += p1.y;
+            f[u][4] += p2.x; f[u][5] += p2.y; f[u][6] += p3.x; f[u][7] += p3.y;
+          }
         }
       }
-      uint4 o;
-      o.x = pack_bf16x2(f[0] * inv, f[1] * inv);
-      o.y = pack_bf16x2(f[2] * inv, f[3] * inv);
-      o.z = pack_bf16x2(f[4] * inv, f[5] * inv);
-      o.w = pack_bf16x2(f[6] * inv, f[7] * inv);
-      // Sum of squares of the values every rank will hold (after bf16 rounding).
-      const float2 q0 = unpack_bf16x2(o.x), q1 = unpack_bf16x2(o.y), q2 = unpack_bf16x2(o.z), q3 = unpack_bf16x2(o.w);
-      sq += q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y + q2.x * q2.x + q2.y * q2.y + q3.x * q3.x + q3.y * q3.y;
-      if (NVLS) {
-        multimem_st_bf16x8(a.mc_base + off, o);
-      } else {
-        for (int r = 0; r < a.world; ++r) st_cg_v4(a.bases[r] + off, o);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (!live[u]) continue;
+        const long long off = a.start + (vb + u * stride) * 8;
+        uint4 o;
+        o.x = pack_bf16x2(f[u][0] * inv, f[u][1] * inv);
+        o.y = pack_bf16x2(f[u][2] * inv, f[u][3] * inv);
+        o.z = pack_bf16x2(f[u][4] * inv, f[u][5] * inv);
+        o.w = pack_bf16x2(f[u][6] * inv, f[u][7] * inv);
+        // Sum of squares of the values every rank will hold (after bf16 rounding).
+        const float2 q0 = unpack_bf16x2(o.x), q1 = unpack_bf16x2(o.y), q2 = unpack_bf16x2(o.z), q3 = unpack_bf16x2(o.w);
+        sq += q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y + q2.x * q2.x + q2.y * q2.y + q3.x * q3.x + q3.y * q3.y;
+        if (NVLS) {
+          multimem_st_bf16x8(a.mc_base + off, o);
+        } else {
+          for (int r = 0; r < a.world; ++r) st_cg_v4(a.bases[r] + off, o);
+        }
       }
     }
   }
@@ -165,9 +181,40 @@ dp_finalize_kernel(const uint32_t* pad, const unsigned int* epochs, int num_buck
   }
 }
 
+// Flat copy with eight 16-byte loads in flight per thread: a probe of what plain loads from a peer's memory (or from
+// local memory) sustain, used as the link-bandwidth denominator of the fused-path reports.
+__global__ void __launch_bounds__(kDpThreads)
+copy_flat_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nvec) {
+  constexpr int kUnroll = 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long vb = (long long)blockIdx.x * blockDim.x + threadIdx.x; vb < nvec; vb += stride * kUnroll) {
+    uint4 t[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long v = vb + u * stride;
+      t[u] = ld_cg_v4(src + (v < nvec ? v : vb));
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long v = vb + u * stride;
+      if (v < nvec) st_cg_v4(dst + v, t[u]);
+    }
+  }
+}
+
 }  // namespace dptb
 
 using namespace dptb;
+
+// dst[0, nbytes) = src[0, nbytes); both 16-byte aligned, nbytes a multiple of 16; either may be peer-mapped memory.
+extern "C" int dptb_copy_flat(const void* src, void* dst, long long nbytes, int grid, void* stream) {
+  if (nbytes <= 0) return 0;
+  if ((nbytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return kErrBadShape;
+  if (grid <= 0) grid = 4 * sm_count();
+  copy_flat_kernel<<<grid, kDpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), nbytes / 16);
+  return counted(1, (int)cudaGetLastError());
+}
 
 struct DptbDpArgs {
   void* bases[kMaxRanks];

@@ -159,12 +159,14 @@ def layernorm_bwd(x, dy, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, 
     return dx.view(x.shape), dgamma, dbeta
 
 
-def rmsnorm_fwd(x, gamma, eps):
+def rmsnorm_fwd(x, gamma, eps, out=None):
     lib = N.load()
     D = x.shape[-1]
     x2 = x.reshape(-1, D)
     rows = x2.shape[0]
-    y = torch.empty_like(x2)
+    y = torch.empty_like(x2) if out is None else out.reshape(-1, D)
+    if y.shape != x2.shape or y.dtype != x2.dtype or not y.is_contiguous():
+        raise ValueError("rmsnorm_fwd: `out` must be a contiguous tensor of the input's shape and dtype")
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
     N.check(lib.dptb_rmsnorm_fwd(x2.data_ptr(), gamma.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, D, eps,
                                  N.dtype_code(x2), N.stream_ptr()), "rmsnorm_fwd")
@@ -411,6 +413,19 @@ def copy2d(src: torch.Tensor, dst: torch.Tensor, rows: int, cols: int):
     lib = N.load()
     N.check(lib.dptb_copy2d(src.data_ptr(), _lead(src), dst.data_ptr(), _lead(dst), rows, cols, N.dtype_code(src),
                             N.stream_ptr()), "copy2d")
+    return dst
+
+
+def copy_flat(src: torch.Tensor, dst: torch.Tensor, grid: int = 0):
+    """``dst[:] = src[:]`` for contiguous tensors of equal byte size (a multiple of 16), by a kernel that keeps eight
+    16-byte loads in flight per thread; either side may be another GPU's memory mapped into this process."""
+    lib = N.load()
+    nbytes = src.numel() * src.element_size()
+    if nbytes != dst.numel() * dst.element_size() or not (src.is_contiguous() and dst.is_contiguous()):
+        raise ValueError("copy_flat: contiguous tensors of equal byte size")
+    lib.dptb_copy_flat.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p]
+    lib.dptb_copy_flat.restype = ctypes.c_int
+    N.check(lib.dptb_copy_flat(src.data_ptr(), dst.data_ptr(), nbytes, grid, N.stream_ptr()), "copy_flat")
     return dst
 
 

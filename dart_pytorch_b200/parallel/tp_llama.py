@@ -12,7 +12,11 @@ width.  Per block and rank:
     y   = rmsnorm(x');  h = silu(y Wg_r^T) * (y Wu_r^T)
     x   = x' + sum_r(h_r @ Wd_r^T)                    row-parallel: ONE kernel again
 
-The residual stream ping-pongs between two symmetric activation buffers.  The output head is vocabulary-sharded; the
+The residual stream ping-pongs between two symmetric activation buffers.  Prefill also has a sequence-parallel schedule
+(``prefill(..., mode="sp")``): the residual stream is sharded by rows, every rank normalises only its rows, the
+column-parallel GEMMs read the peers' normalised rows in place (all-gather fused into the GEMM's operand loads) and the
+row-parallel GEMMs end in a reduce-scatter instead of an all-reduce, which halves the NVLink bytes per projection pair
+and divides the norm work by the group size.  The output head is vocabulary-sharded; the
 greedy token is picked by one kernel that exchanges per-rank (max, index) pairs through peer memory, so a decode step
 never returns to the host and is captured in a CUDA graph (the position lives in device memory).
 """
@@ -63,7 +67,8 @@ class TPLlamaEngine:
         self.hd = c.head_dim
         self.Hq, self.Hkv, self.F, self.Vl = c.num_heads // T, c.num_kv_heads // T, c.ffn_dim // T, c.vocab_size // T
         self.max_batch, self.max_ctx, self.max_rows = max_batch, max_ctx, max_rows
-        self.comm = TpComm(max_rows, c.embed_dim, group=self.group, num_bufs=2, use_nvls=use_nvls)
+        # three activation buffers: the sequence-parallel prefill keeps x, norm(x) and x' apart
+        self.comm = TpComm(max_rows, c.embed_dim, group=self.group, num_bufs=3, use_nvls=use_nvls)
         self.lib = N.load()
         self.lib.dptb_tp_argmax.argtypes = [ctypes.POINTER(TpArgmaxArgs), c_void_p]
         self.lib.dptb_tp_argmax.restype = c_int
@@ -174,6 +179,54 @@ class TPLlamaEngine:
             x = self.comm.gemm_allreduce(h, L.w_down, 0, residual=x1)
         return x
 
+    def _blocks_sp(self, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        """Sequence-parallel schedule of ``_blocks`` for a prefill from position 0.  ``x``: this rank's rows
+        ``[rank * M / T, (rank + 1) * M / T)`` of the embedded tokens, in activation buffer 0 (first ``M / T`` rows);
+        returns this rank's rows of the final residual stream (same place).  Buffer 1 holds the normalised rows the
+        peers read, buffer 2 the post-attention residual.  A buffer is rewritten only after a reduce-scatter GEMM has
+        completed in between: that kernel ends with a handshake of all ranks, so every rank's earlier reads are over."""
+        c, hd, Hq, Hkv = self.config, self.hd, self.Hq, self.Hkv
+        M = B * S
+        Ms = M // self.T
+        dq = Hq * hd
+        for L in self.layers:
+            y = self.comm.buffer(1, Ms)
+            K.rmsnorm_fwd(x, L.attn_norm, c.rms_norm_eps, out=y)
+            self.comm.publish_shard()
+            qkv = torch.empty(M, (Hq + 2 * Hkv) * hd, dtype=torch.bfloat16, device=self.dev)
+            self.comm.allgather_gemm(1, Ms, L.w_qkv, qkv)
+            D.rope_kv_append(qkv, L.k_cache, L.v_cache, B, S, Hq, Hkv, hd, 0, base=c.rope_base, pos=None)
+            kf = L.k_cache.view(-1, Hkv * hd)
+            vf = L.v_cache.view(-1, Hkv * hd)
+            o, _ = flash.attn_fwd(qkv[:, :dq], kf, vf, B, S, S, Hq, Hkv, hd, True, q_offset=0, need_lse=False,
+                                  kv_batch_rows=self.max_ctx)
+            x1 = self.comm.gemm_reduce_scatter(o, L.wo, 2, residual=x)
+            y2 = self.comm.buffer(1, Ms)
+            K.rmsnorm_fwd(x1, L.ffn_norm, c.rms_norm_eps, out=y2)
+            self.comm.publish_shard()
+            gu = torch.empty(M, 2 * self.F, dtype=torch.bfloat16, device=self.dev)
+            self.comm.allgather_gemm(1, Ms, L.w_gate_up, gu)
+            h = K.swiglu_fwd(gu[:, :self.F], gu[:, self.F:])
+            x = self.comm.gemm_reduce_scatter(h, L.w_down, 0, residual=x1)
+        return x
+
+    def _gather_last_rows(self, nb: int, S: int) -> torch.Tensor:
+        """Last-token rows ``[nb, D]`` of a row-sharded residual stream in buffer 0: each row is fetched from the rank
+        that owns it with this package's gather kernel reading the peer's buffer in place (plain loads over NVLink)."""
+        M = nb * S
+        Ms = M // self.T
+        out = torch.empty(nb, self.config.embed_dim, dtype=torch.bfloat16, device=self.dev)
+        rows = torch.arange(nb, device=self.dev) * S + (S - 1)
+        h = self.comm._h_bufs[0]
+        for r in range(self.T):
+            sel = ((rows >= r * Ms) & (rows < (r + 1) * Ms)).nonzero().view(-1)
+            if sel.numel() == 0:
+                continue
+            src = self.comm.bufs[0] if r == self.rank else \
+                h.get_buffer(r, (self.comm.max_rows, self.comm.width), torch.bfloat16)
+            out[sel] = K.embedding_fwd(src[:Ms], (rows[sel] - r * Ms))
+        return out
+
     def _head(self, x_last: torch.Tensor, B: int, advance: int) -> None:
         xf, _ = K.rmsnorm_fwd(x_last, self.final_norm, self.config.rms_norm_eps)
         K.gemm(xf, self.head, self.logits[:B], trans_b=True)
@@ -185,9 +238,14 @@ class TPLlamaEngine:
         self.pos.zero_()
 
     @torch.no_grad()
-    def prefill(self, tokens: torch.Tensor, chunk: Optional[int] = None) -> torch.Tensor:
+    def prefill(self, tokens: torch.Tensor, chunk: Optional[int] = None, mode: str = "ar") -> torch.Tensor:
         """``tokens [B, S]`` (the same on every rank).  Fills the caches and returns the first generated token ids
-        ``[B]`` (device).  Sequences are processed ``chunk`` at a time so the rows of a call fit ``max_rows``."""
+        ``[B]`` (device).  Sequences are processed ``chunk`` at a time so the rows of a call fit ``max_rows``.
+        ``mode``: "ar" keeps activations replicated (GEMM + all-reduce); "sp" shards them by rows (GEMM +
+        reduce-scatter, all-gather + GEMM) and needs the rows of a call to split into whole 128-row tiles per rank
+        (it falls back to "ar" for chunks that do not)."""
+        if mode not in ("ar", "sp"):
+            raise ValueError("prefill: mode must be 'ar' or 'sp'")
         B, S = tokens.shape
         if B > self.max_batch or S > self.max_ctx:
             raise ValueError("prefill: batch or sequence exceeds the engine's capacity")
@@ -201,18 +259,28 @@ class TPLlamaEngine:
         for b0 in range(0, B, chunk):
             b1 = min(B, b0 + chunk)
             nb = b1 - b0
-            x = self.comm.buffer(0, nb * S)
-            x.copy_(K.embedding_fwd(self.embed, tokens[b0:b1].reshape(-1)))
+            sp = mode == "sp" and self.T > 1 and (nb * S) % (self.T * 128) == 0
+            if sp:
+                Ms = nb * S // self.T
+                x = self.comm.buffer(0, Ms)
+                x.copy_(K.embedding_fwd(self.embed, tokens[b0:b1].reshape(-1)[self.rank * Ms:(self.rank + 1) * Ms]))
+            else:
+                x = self.comm.buffer(0, nb * S)
+                x.copy_(K.embedding_fwd(self.embed, tokens[b0:b1].reshape(-1)))
             views = []
             for L in self.layers:      # the chunk's sequences address their own cache rows
                 views.append((L.k_cache, L.v_cache))
                 L.k_cache, L.v_cache = L.k_cache[b0:b1], L.v_cache[b0:b1]
             try:
-                xo = self._blocks(x, nb, S, 0, device_pos=False)
+                xo = self._blocks_sp(x, nb, S) if sp else self._blocks(x, nb, S, 0, device_pos=False)
             finally:
                 for L, (kc, vc) in zip(self.layers, views):
                     L.k_cache, L.v_cache = kc, vc
-            last[b0:b1] = xo.view(nb, S, -1)[:, -1, :]
+            if sp:
+                last[b0:b1] = self._gather_last_rows(nb, S)
+                dist.barrier(group=self.group)     # peers have fetched their rows before buffer 0 is reused
+            else:
+                last[b0:b1] = xo.view(nb, S, -1)[:, -1, :]
         self.seq_len = S
         self.pos.fill_(S)
         self._head(last, B, advance=0)

@@ -61,6 +61,27 @@ def main():
     assert torch.equal(out, eager_seq)
     torch.cuda.synchronize()
     _native.raise_on_device_error()
+    # sequence-parallel prefill (row-sharded activations: reduce-scatter / all-gather GEMMs) against the whole model
+    # and against the all-reduce schedule; the rows of the call split into whole 128-row tiles per rank
+    B2, S2 = 2 * world, 64
+    eng2 = TPLlamaEngine(cfg, max_batch=B2, max_ctx=96, max_rows=B2 * S2, full_model=ref)
+    p2 = torch.randint(0, cfg.vocab_size, (B2, S2), generator=g).cuda()
+    with torch.no_grad():
+        want = ref(p2)[:, -1, :].float()
+    firsts = {}
+    for mode in ("sp", "ar", "sp"):
+        eng2.reset()
+        firsts[mode] = eng2.prefill(p2, mode=mode).clone()
+        got = full_logits(eng2, B2)
+        err = (got - want).abs().max().item()
+        assert err < 0.06 * want.abs().max().item() + 0.02, f"prefill mode {mode}: logits differ by {err}"
+    nxt = eng2.decode_step(B2, use_graph=False).clone()        # the caches the sp prefill filled serve decode
+    with torch.no_grad():
+        want2 = ref(torch.cat([p2, firsts["sp"].view(B2, 1)], 1))[:, -1, :].float()
+    err = (full_logits(eng2, B2) - want2).abs().max().item()
+    assert err < 0.06 * want2.abs().max().item() + 0.02, f"decode after sp prefill: logits differ by {err}"
+    torch.cuda.synchronize()
+    _native.raise_on_device_error()
     dist.barrier()
     if rank == 0:
         print(f"tp_llama_worker ok (hd={hd}, nvls={eng.comm.use_nvls})")
