@@ -128,6 +128,66 @@ ce_bwd_kernel(const T* logits, long long ld, const long long* __restrict__ targe
   }
 }
 
+// Loss and gradient in ONE pass over HBM.  A CTA holds a row of logits in shared memory: it streams the row in while
+// folding (max, sum exp) online, derives the row's log-sum-exp and loss, then writes (softmax - onehot) * scale back
+// over the row from shared memory.  The logits are read once and written once (the two-kernel path reads them twice);
+// what the gradient is later multiplied with (the upstream scalar of the mean loss) is applied by the caller to the
+// small operands of the following GEMMs.  Requires the row (pad_to elements) to fit in shared memory and vector access.
+constexpr int kCeFusedThreads = 512;
+template <typename T>
+__global__ void __launch_bounds__(kCeFusedThreads)
+ce_fused_kernel(T* logits, long long ld, const long long* __restrict__ targets, float* __restrict__ loss,
+                float* __restrict__ lse_out, float scale, long long rows, int V, int pad_to) {
+  extern __shared__ __align__(16) unsigned char ce_row_raw[];
+  T* srow = reinterpret_cast<T*>(ce_row_raw);
+  __shared__ float scratch[66];
+  const int nvec_v = V / 8;          // whole vectors inside the vocabulary
+  const int nvec = pad_to / 8;       // vectors to write (padding columns get zeros)
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    T* xr = logits + r * ld;
+    float m = -INFINITY, s = 0.0f;
+    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+      float v[8];
+      Vec8<T>::load(xr + vi * 8, v);
+      Vec8<T>::store(srow + vi * 8, v);
+      if (vi < nvec_v) {
+        float lm = v[0];
+#pragma unroll
+        for (int j = 1; j < 8; ++j) lm = fmaxf(lm, v[j]);
+        float ls = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ls += __expf(v[j] - lm);
+        online_combine(m, s, lm, ls);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (vi * 8 + j < V) online_combine(m, s, v[j], 1.0f);
+      }
+    }
+    block_online_combine(m, s, scratch);      // contains the barriers that make the staged row visible
+    const float l = m + logf(s);
+    const long long t = targets[r];
+    if (threadIdx.x == 0) {
+      const float picked = (t >= 0 && t < V) ? to_f32(srow[t]) : 0.0f;
+      lse_out[r] = l;
+      loss[r] = (t >= 0 && t < V) ? l - picked : l;
+    }
+    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+      float v[8];
+      Vec8<T>::load(srow + vi * 8, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = vi * 8 + j;
+        float p = c < V ? __expf(v[j] - l) : 0.0f;
+        if (c == t) p -= 1.0f;
+        v[j] = p * scale;
+      }
+      Vec8<T>::store(xr + vi * 8, v);
+    }
+    __syncthreads();                          // the row buffer is reused by the next row
+  }
+}
+
 // y = softmax(x) per row (three passes; rows are L2 resident between passes).
 template <typename T>
 __global__ void __launch_bounds__(kLossThreads)
@@ -194,6 +254,30 @@ extern "C" int dptb_ce_bwd(const void* logits, long long ld, const long long* ta
                      (ld % 8 == 0) && (ldd % 8 == 0) && (pad_to % 8 == 0);
   if (dtype) ce_bwd_kernel<__nv_bfloat16><<<row_grid(rows), kLossThreads, 0, st>>>((const __nv_bfloat16*)logits, ld, targets, lse, g, g_stride, scale, (__nv_bfloat16*)dlogits, ldd, rows, V, pad_to, vec_ok);
   else       ce_bwd_kernel<float><<<row_grid(rows), kLossThreads, 0, st>>>((const float*)logits, ld, targets, lse, g, g_stride, scale, (float*)dlogits, ldd, rows, V, pad_to, vec_ok);
+  return counted(1, (int)cudaGetLastError());
+}
+// Fused loss + in-place gradient (see ce_fused_kernel).  Returns kErrUnsupported when a row does not fit in shared
+// memory or the buffer cannot be accessed in 16-byte vectors: the caller then runs dptb_ce_fwd + dptb_ce_bwd.
+extern "C" int dptb_ce_fused(void* logits, long long ld, const long long* targets, float* loss, float* lse, float scale,
+                             long long rows, int V, int pad_to, int dtype, void* stream) {
+  if (rows <= 0) return 0;
+  if (pad_to < V || pad_to > ld) return kErrBadShape;
+  const size_t esz = dtype ? 2 : 4;
+  const size_t bytes = (size_t)pad_to * esz;
+  if ((reinterpret_cast<uintptr_t>(logits) & 15) || (ld % 8) || (pad_to % 8) || bytes > 200 * 1024) return kErrUnsupported;
+  auto st = static_cast<cudaStream_t>(stream);
+  const int per_sm = bytes <= 100 * 1024 ? 2 : 1;
+  const long long want = (long long)sm_count() * per_sm;
+  const int grid = (int)(rows < want ? rows : want);
+  if (dtype) {
+    auto kern = ce_fused_kernel<__nv_bfloat16>;
+    DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    kern<<<grid, kCeFusedThreads, bytes, st>>>((__nv_bfloat16*)logits, ld, targets, loss, lse, scale, rows, V, pad_to);
+  } else {
+    auto kern = ce_fused_kernel<float>;
+    DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    kern<<<grid, kCeFusedThreads, bytes, st>>>((float*)logits, ld, targets, loss, lse, scale, rows, V, pad_to);
+  }
   return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_softmax_fwd(const void* x, void* y, long long rows, int D, int dtype, void* stream) {

@@ -202,6 +202,27 @@ def ce_fwd(logits2d: torch.Tensor, targets: torch.Tensor, vocab: int):
     return loss, lse
 
 
+def ce_fused(logits2d: torch.Tensor, targets: torch.Tensor, vocab: int, scale: float, pad_to: Optional[int] = None):
+    """Per-row loss and log-sum-exp, and ``(softmax - onehot) * scale`` written IN PLACE over the logits, in one pass
+    (each row is staged in shared memory).  Returns ``(loss, lse)``, or ``None`` when the kernel does not cover the
+    shape (row too long for shared memory, unaligned buffer): nothing was written then."""
+    lib = N.load()
+    rows = logits2d.shape[0]
+    pad_to = vocab if pad_to is None else pad_to
+    loss = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
+    lib.dptb_ce_fused.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                  ctypes.c_float, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                  ctypes.c_void_p]
+    lib.dptb_ce_fused.restype = ctypes.c_int
+    rc = lib.dptb_ce_fused(logits2d.data_ptr(), _lead(logits2d), targets.data_ptr(), loss.data_ptr(), lse.data_ptr(),
+                           float(scale), rows, vocab, pad_to, N.dtype_code(logits2d), N.stream_ptr())
+    if rc == ERR_UNSUPPORTED:
+        return None
+    N.check(rc, "ce_fused")
+    return loss, lse
+
+
 def ce_bwd(logits2d, targets, lse, g, scale: float, vocab: int, out=None, pad_to: Optional[int] = None):
     """``(softmax - onehot) * g[row] * scale`` written to ``out`` (default: in place over ``logits2d``)."""
     lib = N.load()
