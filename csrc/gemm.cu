@@ -600,12 +600,17 @@ __device__ __forceinline__ void epi_half_tma(const GemmParams& p, const uint32_t
           pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
   }
   if (p.act == 2) {
+    // GELU (tanh form) on pairs of values: x * (0.5 + 0.5 tanh(x (c0 + c1 x^2)))
+    const f32x2 c0 = f2_splat(0.7978845608f), c1 = f2_splat(0.0356774081f), hf = f2_splat(0.5f);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float x = v[i];
-      const float u = x * fmaf(x * x, 0.0356774081f, 0.7978845608f);
-      const float hx = 0.5f * x;
-      v[i] = fmaf(hx, tanh_fast(u), hx);
+    for (int i = 0; i < 32; i += 2) {
+      const f32x2 x = f2_pack(v[i], v[i + 1]);
+      const f32x2 u = f2_mul(x, f2_fma(f2_mul(x, x), c1, c0));
+      float u0, u1;
+      f2_unpack(u, u0, u1);
+      const f32x2 t = f2_pack(tanh_fast(u0), tanh_fast(u1));
+      const f32x2 hx = f2_mul(x, hf);
+      f2_unpack(f2_fma(hx, t, hx), v[i], v[i + 1]);
     }
   } else if (p.act >= 1 && p.act <= 4) {
 #pragma unroll
@@ -618,12 +623,21 @@ __device__ __forceinline__ void epi_half_tma(const GemmParams& p, const uint32_t
       unpack8(*reinterpret_cast<const uint4*>(row_c + (((h * 4 + g) ^ (lane & 7)) << 4)), x);
       if (in_kind == 1) {
         if (p.act == 12) {
+          // GELU' on pairs: 0.5 (1 + t) + 0.5 x (1 - t^2) (c0 + c2 x^2),  t = tanh(x (c0 + c1 x^2))
+          const f32x2 c0 = f2_splat(0.7978845608f), c1 = f2_splat(0.0356774081f), c2 = f2_splat(0.1070322243f);
+          const f32x2 one = f2_splat(1.0f), hf = f2_splat(0.5f);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float xx = x[e] * x[e];
-            const float t = tanh_fast(x[e] * fmaf(xx, 0.0356774081f, 0.7978845608f));
-            const float sl = x[e] * fmaf(xx, 0.1070322243f, 0.7978845608f);
-            v[g * 8 + e] *= 0.5f * (1.0f + t + sl * fmaf(-t, t, 1.0f));
+          for (int e = 0; e < 8; e += 2) {
+            const f32x2 xp = f2_pack(x[e], x[e + 1]);
+            const f32x2 xx = f2_mul(xp, xp);
+            float u0, u1;
+            f2_unpack(f2_mul(xp, f2_fma(xx, c1, c0)), u0, u1);
+            const float t0 = tanh_fast(u0), t1 = tanh_fast(u1);
+            const f32x2 t = f2_pack(t0, t1), nt = f2_pack(-t0, -t1);
+            const f32x2 sl = f2_mul(xp, f2_fma(xx, c2, c0));
+            const f32x2 w = f2_fma(sl, f2_fma(nt, t, one), t);          // t + sl (1 - t^2)
+            const f32x2 d = f2_fma(w, hf, hf);                           // 0.5 + 0.5 w
+            f2_unpack(f2_mul(f2_pack(v[g * 8 + e], v[g * 8 + e + 1]), d), v[g * 8 + e], v[g * 8 + e + 1]);
           }
         } else {
           apply_act_bwd8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]), x);
