@@ -301,10 +301,12 @@ struct DptbDecodeArgs {
 extern "C" long long dptb_attn_decode_ws_floats(int B, int Sq, int Hq, int head_dim, int splits) {
   return splits <= 1 ? 0 : (long long)B * Sq * Hq * splits * (head_dim + 2);
 }
-// Split count that fills the GPU: about four CTAs per SM, at least 128 keys (one 32-key block per warp) per CTA.
+// Split count that fills the GPU once: three CTAs fit an SM (registers), and a grid beyond that runs a second, mostly
+// empty wave, so the count is rounded DOWN to what is resident at once; at least 128 keys (one 32-key block per warp)
+// per CTA.
 extern "C" int dptb_attn_decode_splits(int B, int Sq, int Hkv, int Sk) {
   const int base = B * Sq * Hkv;
-  int s = (4 * sm_count() + base - 1) / base;
+  int s = (3 * sm_count()) / base;
   const int cap = (Sk + 127) / 128;
   if (s > cap) s = cap;
   if (s > 64) s = 64;

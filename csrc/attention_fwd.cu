@@ -322,13 +322,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < kAttnBN; ++i)
           if (key0 + i > key_limit) s[i] = 0xff800000u;   // -inf
       }
+      // three-input maxima: half the instructions of the two-input form
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < kAttnBN; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
-        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      for (int i = 0; i < kAttnBN; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
       }
       const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
       ATTN_PROF_MARK(pt3);
@@ -370,10 +371,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
+          // Two of every four exponentials on the special-function unit, two as a polynomial on the FMA pipe: the
+          // softmax of a 64-wide head is bound by the special-function rate otherwise.
           const float a = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 0]), p.scale_log2, -m_sub));
           const float b = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), p.scale_log2, -m_sub));
-          const float e = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 2]), p.scale_log2, -m_sub));
-          const float f = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 3]), p.scale_log2, -m_sub));
+          float e, f;
+          {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(s[c * 32 + i + 2]), __uint_as_float(s[c * 32 + i + 3])),
+                             f2_splat(p.scale_log2), f2_splat(-m_sub)), x0, x1);
+            exp2_poly2(x0, x1, e, f);
+          }
           l0 += a; l1 += b; l2 += e; l3 += f;
           packed[(i >> 1) + 0] = pack_bf16x2(a, b);
           packed[(i >> 1) + 1] = pack_bf16x2(e, f);
@@ -411,7 +419,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) {
         tc_fence_after_sync();
         const bool live = q_row < p.Sq;
-        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        // a row without any visible key keeps m_use = -inf (its polynomial exponentials are 2^-127, not 0)
+        const bool any_key = l_run > 0.0f && m_use != -INFINITY;
+        const float inv = any_key ? 1.0f / l_run : 0.0f;
         __nv_bfloat16* dst = p.o + ((long long)batch * p.Sq + (live ? q_row : 0)) * p.ldo + (long long)head * HD;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
@@ -432,7 +442,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_before_sync();
         if (live && p.lse) {
-          const float lse2 = (l_run > 0.0f) ? m_use + log2f(l_run) : -INFINITY;
+          const float lse2 = any_key ? m_use + log2f(l_run) : -INFINITY;
           p.lse[((long long)batch * p.Hq + head) * p.Sq + q_row] = lse2 * 0.6931471805599453f;
         }
       }

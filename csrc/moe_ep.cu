@@ -33,48 +33,77 @@ constexpr int kMaxExperts = 64;
 constexpr int kMaxTopK = 8;
 
 // ---------------------------------------------------------------------------------------------- routing
-// logits [T, ld] fp32 or bf16 -> probs [T, E] fp32 (softmax), idx [T, k] int32, w [T, k] fp32.
+// logits [T, ld] fp32 or bf16 -> probs [T, E] fp32, idx [T, k] int32, w [T, k] fp32.
+//   gate 0: probs = softmax(logits); gate 1: probs = sigmoid(logits) (reference: lib/core/nn/moe.dart:379-472).
+//   The choice is made on probs + bias (aux-loss-free balancing bias, may be null; the weights stay unbiased).
+//   groups > 1: the experts form `groups` equal groups; a group's score is its best biased score (softmax gate) or the
+//   sum of its two best (sigmoid gate); only experts of the `top_groups` best groups can be chosen.
 template <typename TL>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const TL* __restrict__ logits, long long ld, float* __restrict__ probs, int* __restrict__ idx,
-                 float* __restrict__ w, int T, int E, int k, int renorm, float route_scale) {
+                 float* __restrict__ w, int T, int E, int k, int renorm, float route_scale, int gate,
+                 const float* __restrict__ bias, int groups, int top_groups) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   float p[kMaxExperts];
-  float mx = -INFINITY;
-  for (int e = 0; e < E; ++e) {
-    p[e] = to_f32(logits[(long long)t * ld + e]);
-    mx = fmaxf(mx, p[e]);
+  if (gate == 0) {
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+      p[e] = to_f32(logits[(long long)t * ld + e]);
+      mx = fmaxf(mx, p[e]);
+    }
+    float sum = 0.0f;
+    for (int e = 0; e < E; ++e) {
+      p[e] = __expf(p[e] - mx);
+      sum += p[e];
+    }
+    const float inv = 1.0f / sum;
+    for (int e = 0; e < E; ++e) p[e] *= inv;
+  } else {
+    for (int e = 0; e < E; ++e) p[e] = 1.0f / (1.0f + __expf(-to_f32(logits[(long long)t * ld + e])));
   }
-  float sum = 0.0f;
-  for (int e = 0; e < E; ++e) {
-    p[e] = __expf(p[e] - mx);
-    sum += p[e];
-  }
-  const float inv = 1.0f / sum;
-  for (int e = 0; e < E; ++e) {
-    p[e] *= inv;
-    probs[(long long)t * E + e] = p[e];
+  for (int e = 0; e < E; ++e) probs[(long long)t * E + e] = p[e];
+  // scores the choice is made on; experts of groups that are not kept drop to -inf
+  float sel[kMaxExperts];
+  for (int e = 0; e < E; ++e) sel[e] = p[e] + (bias ? bias[e] : 0.0f);
+  if (groups > 1) {
+    const int per = E / groups;
+    float gs[kMaxExperts];
+    for (int g = 0; g < groups; ++g) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = sel[e];
+        if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+      }
+      gs[g] = (gate == 1 && per >= 2) ? b1 + b2 : b1;
+    }
+    unsigned long long keep = 0ull;
+    for (int j = 0; j < top_groups; ++j) {
+      int best = -1;
+      float bv = -INFINITY;
+      for (int g = 0; g < groups; ++g)
+        if (!((keep >> g) & 1ull) && (best < 0 || gs[g] > bv)) { bv = gs[g]; best = g; }
+      keep |= 1ull << best;
+    }
+    for (int e = 0; e < E; ++e)
+      if (!((keep >> (e / per)) & 1ull)) sel[e] = -INFINITY;
   }
   float wsum = 0.0f;
-  int chosen[kMaxTopK];
+  unsigned long long taken = 0ull;
   for (int j = 0; j < k; ++j) {
-    int best = 0;
-    float bv = -1.0f;
-    for (int e = 0; e < E; ++e) {
-      bool taken = false;
-      for (int q = 0; q < j; ++q) taken |= chosen[q] == e;
-      if (!taken && p[e] > bv) {      // ties resolve to the lowest expert index
-        bv = p[e];
+    int best = -1;
+    float bv = -INFINITY;
+    for (int e = 0; e < E; ++e)
+      if (!((taken >> e) & 1ull) && (best < 0 || sel[e] > bv)) {      // ties resolve to the lowest expert index
+        bv = sel[e];
         best = e;
       }
-    }
-    chosen[j] = best;
+    taken |= 1ull << best;
     idx[(long long)t * k + j] = best;
-    w[(long long)t * k + j] = bv;
-    wsum += bv;
+    w[(long long)t * k + j] = p[best];
+    wsum += p[best];
   }
-  const float s = (renorm ? 1.0f / wsum : 1.0f) * route_scale;
+  const float s = (renorm ? 1.0f / (wsum + 1e-9f) : 1.0f) * route_scale;
   for (int j = 0; j < k; ++j) w[(long long)t * k + j] *= s;
 }
 
@@ -298,13 +327,16 @@ static inline int ep_grid(long long warps) {
 }
 
 extern "C" int dptb_moe_route(const void* logits, long long ld, int logits_f32, float* probs, int* idx, float* w, int T,
-                              int E, int k, int renorm, float route_scale, void* stream) {
+                              int E, int k, int renorm, float route_scale, int gate, const float* bias, int groups,
+                              int top_groups, void* stream) {
   if (T <= 0) return 0;
-  if (E < 1 || E > kMaxExperts || k < 1 || k > kMaxTopK || k > E) return kErrBadShape;
+  if (E < 1 || E > kMaxExperts || k < 1 || k > kMaxTopK || k > E || (gate != 0 && gate != 1)) return kErrBadShape;
+  if (groups < 1) groups = 1;
+  if (groups > 1 && (E % groups || top_groups < 1 || top_groups > groups || k > top_groups * (E / groups))) return kErrBadShape;
   auto st = static_cast<cudaStream_t>(stream);
   const int grid = (T + 255) / 256;
-  if (logits_f32) moe_route_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, ld, probs, idx, w, T, E, k, renorm, route_scale);
-  else moe_route_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, probs, idx, w, T, E, k, renorm, route_scale);
+  if (logits_f32) moe_route_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, ld, probs, idx, w, T, E, k, renorm, route_scale, gate, bias, groups, top_groups);
+  else moe_route_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, probs, idx, w, T, E, k, renorm, route_scale, gate, bias, groups, top_groups);
   return counted(1, (int)cudaGetLastError());
 }
 extern "C" int dptb_moe_slots(const int* idx, int* slot, int* count, int n_pairs, int E, int C, void* stream) {

@@ -51,7 +51,7 @@ def _lib():
     if not _declared:
         P, I, L, Fl = c_void_p, c_int, c_ll, c_float
         EP = ctypes.POINTER(EpArgs)
-        for name, args in (("dptb_moe_route", [P, L, I, P, P, P, I, I, I, I, Fl, P]),
+        for name, args in (("dptb_moe_route", [P, L, I, P, P, P, I, I, I, I, Fl, I, P, I, I, P]),
                            ("dptb_moe_slots", [P, P, P, I, I, I, P]),
                            ("dptb_moe_dispatch", [EP, P, L, P, P, P, P, I, I, P]),
                            ("dptb_moe_zero_tail", [P, P, I, I, I, I, P]),
@@ -145,16 +145,22 @@ class EpComm:
         return dw
 
 
-def route(logits: torch.Tensor, top_k: int, renorm: bool = False, route_scale: float = 1.0):
-    """``(probs [T, E] fp32, idx [T, k] int32, w [T, k] fp32)`` of router logits ``[T, E]`` (fp32 or bf16)."""
+def route(logits: torch.Tensor, top_k: int, renorm: bool = False, route_scale: float = 1.0, gate: str = "softmax",
+          bias: Optional[torch.Tensor] = None, groups: int = 1, top_groups: Optional[int] = None):
+    """``(probs [T, E] fp32, idx [T, k] int32, w [T, k] fp32)`` of router logits ``[T, E]`` (fp32 or bf16).
+    ``gate``: "softmax" or "sigmoid"; ``bias [E]`` fp32 is added to the scores for the choice only; ``groups`` /
+    ``top_groups``: grouped top-k (reference: lib/core/nn/moe.dart:379-472)."""
     lib = _lib()
     T, E = logits.shape
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != E or not bias.is_contiguous()):
+        raise ValueError("route: bias must be a contiguous fp32 vector with one entry per expert")
     probs = torch.empty(T, E, dtype=torch.float32, device=logits.device)
     idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
     w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
     N.check(lib.dptb_moe_route(logits.data_ptr(), logits.stride(0), int(logits.dtype == torch.float32),
                                probs.data_ptr(), idx.data_ptr(), w.data_ptr(), T, E, top_k, int(renorm),
-                               float(route_scale), N.stream_ptr()), "moe_route")
+                               float(route_scale), {"softmax": 0, "sigmoid": 1}[gate], N.ptr(bias), int(groups),
+                               int(groups if top_groups is None else top_groups), N.stream_ptr()), "moe_route")
     return probs, idx, w
 
 
@@ -208,32 +214,35 @@ class EpCombineFn(torch.autograd.Function):
 
 
 class RouteFn(torch.autograd.Function):
-    """Softmax + top-k on the device; gradients flow to the logits through the selected probabilities (and through
-    all probabilities for the auxiliary loss)."""
+    """Gate (softmax or sigmoid) + (grouped, biased) top-k on the device; gradients flow to the logits through the
+    selected probabilities (and through all probabilities for the auxiliary loss)."""
 
     @staticmethod
-    def forward(ctx, logits, top_k, renorm, route_scale):
-        probs, idx, w = route(logits, top_k, renorm, route_scale)
+    def forward(ctx, logits, top_k, renorm, route_scale, gate="softmax", bias=None, groups=1, top_groups=None):
+        probs, idx, w = route(logits, top_k, renorm, route_scale, gate, bias, groups, top_groups)
         ctx.save_for_backward(probs, idx, w)
-        ctx.cfg = (top_k, renorm, route_scale, logits.dtype)
+        ctx.cfg = (top_k, renorm, route_scale, logits.dtype, gate)
         ctx.mark_non_differentiable(idx)
         return probs, idx, w
 
     @staticmethod
     def backward(ctx, d_probs, _, d_w):
         probs, idx, w = ctx.saved_tensors
-        top_k, renorm, route_scale, dtype = ctx.cfg
+        top_k, renorm, route_scale, dtype, gate = ctx.cfg
         dp = torch.zeros_like(probs) if d_probs is None else d_probs.float().clone()
         if d_w is not None:
             li = idx.long()
             sel = torch.gather(probs, 1, li)
             g = d_w.float() * route_scale
             if renorm:
-                s = sel.sum(1, keepdim=True)
+                s = sel.sum(1, keepdim=True) + 1e-9
                 g = (g - (g * sel).sum(1, keepdim=True) / s) / s
             dp.scatter_add_(1, li, g)
-        dlogits = probs * (dp - (dp * probs).sum(1, keepdim=True))
-        return dlogits.to(dtype), None, None, None
+        if gate == "sigmoid":
+            dlogits = dp * probs * (1.0 - probs)
+        else:
+            dlogits = probs * (dp - (dp * probs).sum(1, keepdim=True))
+        return dlogits.to(dtype), None, None, None, None, None, None, None
 
 
 class ExpertParallelMoE(Module):
@@ -243,7 +252,11 @@ class ExpertParallelMoE(Module):
     def __init__(self, dim: int, hidden: int, num_experts: int, top_k: int = 2, capacity_factor: float = 1.25,
                  aux_loss_coef: float = 0.01, tokens_per_rank: int = 0, group=None, renormalize_top_k: bool = False,
                  route_scale: float = 1.0, device=None, seed: int = 0, dtype=torch.bfloat16,
-                 init_std: Optional[float] = None):
+                 init_std: Optional[float] = None, gate_function: str = "softmax", num_expert_groups: int = 1,
+                 top_k_groups: Optional[int] = None, bias_update_rate: float = 0.001):
+        """``gate_function``: "softmax" or "sigmoid"; ``num_expert_groups`` / ``top_k_groups``: grouped top-k;
+        ``bias_update_rate``: step of the aux-loss-free balancing bias (``update_routing_bias``), all as in the
+        single-device layer (reference: lib/core/nn/moe.dart:379-472, 550-569)."""
         super().__init__()
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
@@ -253,6 +266,17 @@ class ExpertParallelMoE(Module):
         self.El = num_experts // self.world
         self.capacity_factor, self.aux_loss_coef = capacity_factor, aux_loss_coef
         self.renorm, self.route_scale = renormalize_top_k, route_scale
+        if gate_function not in ("softmax", "sigmoid"):
+            raise ValueError("ExpertParallelMoE: gate_function must be 'softmax' or 'sigmoid'")
+        if num_expert_groups < 1 or num_experts % num_expert_groups:
+            raise ValueError("ExpertParallelMoE: num_experts must divide into num_expert_groups groups")
+        self.gate_function, self.groups = gate_function, num_expert_groups
+        self.top_groups = num_expert_groups if top_k_groups is None else top_k_groups
+        if not 1 <= self.top_groups <= self.groups or top_k > self.top_groups * (num_experts // self.groups):
+            raise ValueError("ExpertParallelMoE: top_k_groups out of range for top_k")
+        self.bias_update_rate = bias_update_rate
+        self.routing_bias = torch.zeros(num_experts, dtype=torch.float32, device=device)
+        self._expert_load = torch.zeros(num_experts, dtype=torch.float32, device=device)
         # router weights are replicated (same seed on every rank); expert weights are seeded by global expert id
         self.gate = make_param(normal_((num_experts, dim), init_std or 0.02, seed, device, dtype))
         self.w_gate_up: List[torch.Tensor] = []
@@ -280,7 +304,15 @@ class ExpertParallelMoE(Module):
         return self.aux_loss if self.aux_loss_coef else None
 
     def update_routing_bias(self) -> None:
-        """The aux-loss-free bias update belongs to the single-device layer; nothing to do here."""
+        """Aux-loss-free balancing over the whole group: the routed-pair counts of every rank since the last call are
+        summed, the bias of under-loaded experts rises by ``bias_update_rate`` and that of over-loaded ones falls
+        (sign rule), then the counters reset (reference: lib/core/nn/moe.dart:550-569)."""
+        load = self._expert_load.clone()
+        if self.world > 1:
+            dist.all_reduce(load, group=self.group)
+        if float(load.sum()) > 0:
+            self.routing_bias += self.bias_update_rate * torch.sign(load.mean() - load)
+        self._expert_load.zero_()
 
     def _comm_for(self, T: int) -> EpComm:
         C = capacity(T, self.k, self.E, self.capacity_factor)
@@ -295,7 +327,11 @@ class ExpertParallelMoE(Module):
         T = x2.shape[0]
         comm = self._comm_for(T)
         logits = F.linear(x2, self.gate)
-        probs, idx, w = RouteFn.apply(logits, self.k, self.renorm, self.route_scale)
+        if self.routing_bias.device != x2.device:
+            self.routing_bias = self.routing_bias.to(x2.device)
+            self._expert_load = self._expert_load.to(x2.device)
+        probs, idx, w = RouteFn.apply(logits, self.k, self.renorm, self.route_scale, self.gate_function,
+                                      self.routing_bias, self.groups, self.top_groups)
         slot, count = slots(idx, self.E, comm.C)
         rows_in, counts_here = EpDispatchFn.apply(x2, comm, idx, slot, count)
         per = self.world * comm.C
@@ -308,7 +344,9 @@ class ExpertParallelMoE(Module):
         y = EpCombineFn.apply(rows_out, w, comm, idx, slot, count, counts_here)
         # load-balance auxiliary loss: E * sum_e f_e * P_e, f_e from the routed (not yet capacity-clipped) pairs
         with torch.no_grad():
-            f = torch.bincount(idx.reshape(-1).long(), minlength=self.E).float() / float(T * self.k)
+            counts = torch.bincount(idx.reshape(-1).long(), minlength=self.E).float()
+            self._expert_load += counts
+            f = counts / float(T * self.k)
             self.last_dropped = int((slot < 0).sum().item()) if not torch.cuda.is_current_stream_capturing() else None
         self.aux_loss = self.aux_loss_coef * self.E * (f * probs.mean(0)).sum()
         return y.reshape(shape)

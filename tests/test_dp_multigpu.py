@@ -22,7 +22,8 @@ def _run(mode: str, nproc: int = 2, port: int = 29533):
 def _worlds():
     """Rank counts to test: 2, 4 and 8 as far as the machine has GPUs."""
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    return [w for w in (2, 4, 8) if w <= n] or [2]
+    only = [int(w) for w in os.environ.get("DPTB200_TEST_WORLDS", "").split(",") if w]      # e.g. "8": just that size
+    return [w for w in (2, 4, 8) if w <= n and (not only or w in only)] or [2]
 
 
 needs2 = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")

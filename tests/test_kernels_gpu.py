@@ -215,7 +215,7 @@ def test_cross_entropy_fused_loss_and_gradient(dtype, rows, V, ld):
     ref = R.cross_entropy(xf, tgt)
     ref.mean().backward()
     out = K.ce_fused(buf, tgt, V, 1.0 / rows, pad_to=ld)
-    if ld * buf.element_size() > 200 * 1024:        # a row must fit in shared memory: declined, nothing written
+    if 2 * ld * buf.element_size() > 220 * 1024:    # two rows must fit in shared memory: declined, nothing written
         assert out is None
         return
     assert out is not None
@@ -320,3 +320,32 @@ def test_gemm_split_k_matches_and_is_deterministic(M, N, Kd, trans_a, trans_b, s
     acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
     K.gemm(a, b, acc, trans_a=trans_a, trans_b=trans_b, accumulate=True, splits=splits, bn=bn)
     assert _rel_err(acc, af @ bf + 1.0) < 1e-2
+
+
+@pytest.mark.parametrize("gate,groups,top_groups,k", [("softmax", 1, 1, 2), ("sigmoid", 1, 1, 2), ("sigmoid", 4, 2, 3),
+                                                      ("softmax", 4, 2, 2)])
+def test_moe_route_gate_bias_and_grouped_topk(gate, groups, top_groups, k):
+    """The expert-parallel router against the routing rule of the single-device layer: gate function, choice on
+    score + bias, grouped top-k, weights from the unbiased scores, renormalisation."""
+    from dart_pytorch_b200.parallel import ep
+    T, E = 257, 16
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    bias = torch.randn(E, device="cuda", generator=g) * 0.3
+    probs, idx, w = ep.route(logits, k, renorm=True, route_scale=1.5, gate=gate, bias=bias, groups=groups,
+                             top_groups=top_groups)
+    scores = torch.softmax(logits, -1) if gate == "softmax" else torch.sigmoid(logits)
+    assert _rel_err(probs, scores) < 1e-5
+    biased = scores + bias
+    if groups > 1:
+        per = E // groups
+        grp = biased.view(T, groups, per)
+        gscore = grp.topk(2, -1).values.sum(-1) if gate == "sigmoid" else grp.max(-1).values
+        keep = torch.zeros(T, groups, dtype=torch.bool, device="cuda")
+        keep.scatter_(1, gscore.topk(top_groups, -1).indices, True)
+        biased = torch.where(keep.unsqueeze(-1).expand(T, groups, per).reshape(T, E), biased,
+                             torch.full_like(biased, float("-inf")))
+    want_idx = biased.topk(k, -1).indices
+    assert torch.equal(idx.long().sort(-1).values, want_idx.sort(-1).values)
+    sel = torch.gather(scores, 1, idx.long())
+    assert _rel_err(w, sel / (sel.sum(-1, keepdim=True) + 1e-9) * 1.5) < 1e-5
