@@ -129,9 +129,6 @@ def build_cases(dev, want=()):
         gone = torch.ones(1, device=dev, dtype=torch.float32)
         cases["ce_fwd"] = (lambda: K.ce_fwd(logits, tgt, V), 2 * M * VP, 0.0)
         cases["ce_bwd"] = (lambda: K.ce_bwd(logits, tgt, lse_ce, gone, 1.0 / M, V, out=logits, pad_to=VP), 4 * M * VP, 0.0)
-        # what the training step runs: loss and in-place gradient in one pass (fresh logits each call would be the
-        # real input; the values do not change the traffic)
-        cases["ce_fused"] = (lambda: K.ce_fused(logits, tgt, V, 1.0 / M, pad_to=VP), 4 * M * VP, 0.0)
 
     for cols in (D, 3 * D, 4 * D) if on("colsum") else ():
         src = torch.randn(M, cols, **bf)

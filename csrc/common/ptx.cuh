@@ -402,39 +402,10 @@ __device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
   return d;
 }
 __device__ __forceinline__ f32x2 f2_splat(float x) { return f2_pack(x, x); }
-__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-__device__ __forceinline__ f32x2 f2_add_round_down(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-// 2^x for two values x <= 0 on the FMA pipe instead of the special-function unit (which a softmax saturates long before
-// the tensor cores): x = n + f with n = floor(x) taken from the mantissa of x + 1.5 * 2^23 (rounded down), 2^f from a
-// cubic on [0, 1) (relative error 9e-5, below bf16 resolution), and n added into the exponent field.  x is clamped at
-// -127, where the result is 2^-127 ~ 0.
-__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& y0, float& y1) {
-  const f32x2 magic = f2_splat(12582912.0f);
-  const f32x2 x = f2_pack(fmaxf(x0, -127.0f), fmaxf(x1, -127.0f));
-  const f32x2 xr = f2_add_round_down(x, magic);
-  const f32x2 fl = f2_add(xr, f2_splat(-12582912.0f));
-  const f32x2 fr = f2_fma(fl, f2_splat(-1.0f), x);
-  f32x2 pl = f2_fma(fr, f2_splat(0.077119089663028717041015625f), f2_splat(0.227564394474029541015625f));
-  pl = f2_fma(pl, fr, f2_splat(0.695146143436431884765625f));
-  pl = f2_fma(pl, fr, f2_splat(1.0f));
-  float r0, r1, p0, p1;
-  f2_unpack(xr, r0, r1);
-  f2_unpack(pl, p0, p1);
-  y0 = __uint_as_float((__float_as_uint(r0) << 23) + __float_as_uint(p0));
-  y1 = __uint_as_float((__float_as_uint(r1) << 23) + __float_as_uint(p1));
 }
 
 // ----------------------------------------------------------------------------- packing

@@ -310,16 +310,7 @@ class LMHeadLossFn(torch.autograd.Function):
         logits = torch.empty(M, vpad, dtype=h.dtype, device=h.device)
         K.gemm(h2, w, logits, trans_b=True, n_cols=V)
         tgt = targets.reshape(-1).to(torch.long)
-        # With a backward pass to come, loss and gradient are produced in one pass over the logits: the buffer then
-        # already holds (softmax - onehot) / M when forward returns, and backward only multiplies by the upstream scalar.
-        fused = None
-        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
-            fused = K.ce_fused(logits, tgt, V, 1.0 / M, pad_to=vpad)
-        if fused is None:
-            loss_rows, lse = K.ce_fwd(logits, tgt, V)
-        else:
-            loss_rows, lse = fused
-        ctx.grad_ready = fused is not None
+        loss_rows, lse = K.ce_fwd(logits, tgt, V)
         loss = K.mean_f32(loss_rows)
         ctx.save_for_backward(h2, logits, tgt, lse)
         ctx.w = w
@@ -332,20 +323,14 @@ class LMHeadLossFn(torch.autograd.Function):
         w = ctx.w
         M, V = h2.shape[0], w.shape[0]
         gg = g.reshape(1).float().contiguous()
-        if not ctx.grad_ready:
-            K.ce_bwd(logits, tgt, lse, gg, 1.0 / M, V, pad_to=logits.shape[1])  # in place
+        K.ce_bwd(logits, tgt, lse, gg, 1.0 / M, V, pad_to=logits.shape[1])  # in place
         dl = logits[:, :V]
-        # grad_ready: dl was written without the upstream scalar g (1 for a plain loss.backward()); g stays on the
-        # device (no host read: this runs under graph capture) and multiplies the small operands instead.
-        gs = gg.to(h2.dtype) if ctx.grad_ready else None
         dh = None
         if ctx.needs_input_grad[0]:
             dh = torch.empty_like(h2)
             K.gemm(dl, w, dh)
-            if gs is not None:
-                dh.mul_(gs)
             dh = dh.view(ctx.hshape)
-        dw = _weight_grad(dl, h2 if gs is None else h2 * gs, w, ctx.needs_input_grad[1])
+        dw = _weight_grad(dl, h2, w, ctx.needs_input_grad[1])
         return dh, dw, None
 
 

@@ -202,27 +202,6 @@ def ce_fwd(logits2d: torch.Tensor, targets: torch.Tensor, vocab: int):
     return loss, lse
 
 
-def ce_fused(logits2d: torch.Tensor, targets: torch.Tensor, vocab: int, scale: float, pad_to: Optional[int] = None):
-    """Per-row loss and log-sum-exp, and ``(softmax - onehot) * scale`` written IN PLACE over the logits, in one pass
-    (each row is staged in shared memory).  Returns ``(loss, lse)``, or ``None`` when the kernel does not cover the
-    shape (row too long for shared memory, unaligned buffer): nothing was written then."""
-    lib = N.load()
-    rows = logits2d.shape[0]
-    pad_to = vocab if pad_to is None else pad_to
-    loss = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
-    lse = torch.empty(rows, dtype=torch.float32, device=logits2d.device)
-    lib.dptb_ce_fused.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
-                                  ctypes.c_float, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                  ctypes.c_void_p]
-    lib.dptb_ce_fused.restype = ctypes.c_int
-    rc = lib.dptb_ce_fused(logits2d.data_ptr(), _lead(logits2d), targets.data_ptr(), loss.data_ptr(), lse.data_ptr(),
-                           float(scale), rows, vocab, pad_to, N.dtype_code(logits2d), N.stream_ptr())
-    if rc == ERR_UNSUPPORTED:
-        return None
-    N.check(rc, "ce_fused")
-    return loss, lse
-
-
 def ce_bwd(logits2d, targets, lse, g, scale: float, vocab: int, out=None, pad_to: Optional[int] = None):
     """``(softmax - onehot) * g[row] * scale`` written to ``out`` (default: in place over ``logits2d``)."""
     lib = N.load()
@@ -391,8 +370,23 @@ def unary_bwd(x: torch.Tensor, dy: torch.Tensor, op: str, param: float = 0.0) ->
     return dx
 
 
+_colsum_ws = {}
+
+
+def _colsum_workspace(device, floats: int):
+    """Per-device scratch of the single-launch column sum: fp32 partials and 64 self-resetting counters (zeroed once).
+    Launches that share it are ordered by the stream they run on, like the split-K workspace of the GEMM."""
+    key = (device.type, device.index)
+    ws = _colsum_ws.get(key)
+    if ws is None or ws[0].numel() < floats:
+        ws = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
+              torch.zeros(64, dtype=torch.int32, device=device))
+        _colsum_ws[key] = ws
+    return ws
+
+
 def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False, n_cols=None):
-    """Column sums of a 2-D tensor (bias gradients), deterministic two-stage."""
+    """Column sums of a 2-D tensor (bias gradients), deterministic: fixed row slices, folded in slice order."""
     lib = N.load()
     rows = x2d.shape[0]
     cols = x2d.shape[1] if n_cols is None else n_cols
@@ -402,6 +396,22 @@ def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bo
     if x2d.dtype == torch.bfloat16 and cols % 8 == 0:
         # 16-byte path: about four 256-column CTAs per SM, at least 32 rows each
         nparts = max(1, min(256, 592 // ((cols + 255) // 256), (rows + 31) // 32))
+        # The shared scratch is created outside graph capture only (memory of a capture's private pool must not be
+        # cached); a capture that meets no scratch of sufficient size takes the two-launch form below.
+        key = (x2d.device.type, x2d.device.index)
+        have = key in _colsum_ws and _colsum_ws[key][0].numel() >= nparts * cols
+        if out.dtype == torch.bfloat16 and cols <= 64 * 256 and (have or not torch.cuda.is_current_stream_capturing()):
+            partial, counters = _colsum_workspace(x2d.device, nparts * cols)
+            lib.dptb_colsum_fused.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+            lib.dptb_colsum_fused.restype = ctypes.c_int
+            rc = lib.dptb_colsum_fused(x2d.data_ptr(), _lead(x2d), out.data_ptr(), partial.data_ptr(),
+                                       counters.data_ptr(), rows, cols, nparts, int(accumulate), N.dtype_code(x2d),
+                                       N.stream_ptr())
+            if rc != ERR_UNSUPPORTED:
+                N.check(rc, "colsum_fused")
+                return out
     else:
         nparts = max(1, min(48, (rows + 255) // 256))
     partial = torch.empty(nparts * cols, dtype=torch.float32, device=x2d.device)
