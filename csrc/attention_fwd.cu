@@ -373,7 +373,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int i = 0; i < 32; i += 4) {
           // (Computing half of the exponentials as cubic polynomials on the FMA pipe was measured slower here: 117 us
           // against 102 us at B16 H12 S1024 hd64; the softmax warps are bound by issue slots, not by the
-          // special-function unit.)
+          // special-function unit.  Taking the exponentials two at a time in bf16, ex2.approx.bf16x2, was slower as
+          // well, 115 us, for the unpacking its row sum needs.)
           const float a = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 0]), p.scale_log2, -m_sub));
           const float b = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 1]), p.scale_log2, -m_sub));
           const float e = fast_exp2(fmaf(__uint_as_float(s[c * 32 + i + 2]), p.scale_log2, -m_sub));

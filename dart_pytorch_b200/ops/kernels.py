@@ -370,21 +370,6 @@ def unary_bwd(x: torch.Tensor, dy: torch.Tensor, op: str, param: float = 0.0) ->
     return dx
 
 
-_colsum_ws = {}
-
-
-def _colsum_workspace(device, floats: int):
-    """Per-device scratch of the single-launch column sum: fp32 partials and 64 self-resetting counters (zeroed once).
-    Launches that share it are ordered by the stream they run on, like the split-K workspace of the GEMM."""
-    key = (device.type, device.index)
-    ws = _colsum_ws.get(key)
-    if ws is None or ws[0].numel() < floats:
-        ws = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
-              torch.zeros(64, dtype=torch.int32, device=device))
-        _colsum_ws[key] = ws
-    return ws
-
-
 def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False, n_cols=None):
     """Column sums of a 2-D tensor (bias gradients), deterministic: fixed row slices, folded in slice order."""
     lib = N.load()
@@ -396,22 +381,6 @@ def colsum(x2d: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bo
     if x2d.dtype == torch.bfloat16 and cols % 8 == 0:
         # 16-byte path: about four 256-column CTAs per SM, at least 32 rows each
         nparts = max(1, min(256, 592 // ((cols + 255) // 256), (rows + 31) // 32))
-        # The shared scratch is created outside graph capture only (memory of a capture's private pool must not be
-        # cached); a capture that meets no scratch of sufficient size takes the two-launch form below.
-        key = (x2d.device.type, x2d.device.index)
-        have = key in _colsum_ws and _colsum_ws[key][0].numel() >= nparts * cols
-        if out.dtype == torch.bfloat16 and cols <= 64 * 256 and (have or not torch.cuda.is_current_stream_capturing()):
-            partial, counters = _colsum_workspace(x2d.device, nparts * cols)
-            lib.dptb_colsum_fused.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p,
-                                              ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
-                                              ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
-            lib.dptb_colsum_fused.restype = ctypes.c_int
-            rc = lib.dptb_colsum_fused(x2d.data_ptr(), _lead(x2d), out.data_ptr(), partial.data_ptr(),
-                                       counters.data_ptr(), rows, cols, nparts, int(accumulate), N.dtype_code(x2d),
-                                       N.stream_ptr())
-            if rc != ERR_UNSUPPORTED:
-                N.check(rc, "colsum_fused")
-                return out
     else:
         nparts = max(1, min(48, (rows + 255) // 256))
     partial = torch.empty(nparts * cols, dtype=torch.float32, device=x2d.device)
