@@ -83,11 +83,11 @@ def build_cases(dev, want=()):
 
     gemm_case("gemm_qkv_fwd", M, 3 * D, D, False, True, bias=True)
     gemm_case("gemm_proj_fwd", M, D, D, False, True, bias=True, residual=True)
-    gemm_case("gemm_fc1_fwd_gelu", M, 4 * D, D, False, True, bias=True, act="gelu_tanh", aux_out=True)
+    gemm_case("gemm_fc1_fwd_gelu", M, 4 * D, D, False, True, bias=True, act="gelu_tanh_d", aux_out=True)
     gemm_case("gemm_fc2_fwd", M, D, 4 * D, False, True, bias=True, residual=True)
     gemm_case("gemm_lmhead_fwd", M, VP, D, False, True)
     gemm_case("gemm_fc1_dgrad", M, D, 4 * D, False, False)
-    gemm_case("gemm_fc2_dgrad", M, 4 * D, D, False, False, act_bwd="gelu_tanh")
+    gemm_case("gemm_fc2_dgrad", M, 4 * D, D, False, False, act_bwd="mul")
     gemm_case("gemm_qkv_dgrad", M, D, 3 * D, False, False)
     gemm_case("gemm_fc1_wgrad", 4 * D, D, M, True, False, accumulate=True)
     gemm_case("gemm_fc2_wgrad", D, 4 * D, M, True, False, accumulate=True)

@@ -6,7 +6,8 @@
 Config (random N(0, 0.02) weights, uniform random prompts, bf16): 32 layers, d 4096, 32 query / 8 KV heads, head 128,
 RoPE theta 500000, RMSNorm eps 1e-5, SwiGLU ffn 14336, vocab 128256; batch 32 prompts x 2048 tokens prefill, then 256
 greedy decode steps.  ``--impl ours`` runs ``TPLlamaEngine`` (fused GEMM + all-reduce kernels, CUDA-graph decode);
-``--impl torch`` runs the same sharding with cuBLAS matmuls, SDPA and NCCL all-reduces (the library baseline).
+``--impl torch`` runs the same sharding with cuBLAS matmuls, SDPA and NCCL all-reduces (the library baseline), its
+decode step with static shapes replayed as a CUDA graph like ours (``--no-graph`` times it eagerly).
 Times are CUDA events on the launching stream, max over ranks; rank 0 prints one JSON line.
 """
 from __future__ import annotations

@@ -151,7 +151,8 @@ __device__ __forceinline__ float sigmoid_fast(float x) { return 1.0f / (1.0f + _
 __device__ __forceinline__ float act_fwd(int act, float x) {
   switch (act) {
     case 1: return fmaxf(x, 0.0f);
-    case 2: {
+    case 2:
+    case 5: {
       float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
       return 0.5f * x * (1.0f + tanh_fast(u));
     }
@@ -176,16 +177,20 @@ __device__ __forceinline__ float act_bwd(int act, float x) {
       float s = sigmoid_fast(x);
       return s * (1.0f + x * (1.0f - s));
     }
+    case 15: return x;   // the saved tensor already is the derivative (see act code 5)
     default: return 1.0f;
   }
 }
+// What the auxiliary output receives: the pre-activation value, or (act code 5, the training MLP) the GELU derivative
+// at that value, so that the backward GEMM's epilogue is one multiply per element instead of a second tanh.
+__device__ __forceinline__ float aux_value(int act, float x) { return act == 5 ? act_bwd(12, x) : x; }
 
 // One output element, used by the tail path of the tensor-core kernel and by the SIMT kernel.
 __device__ __forceinline__ void epilogue_scalar(const GemmParams& p, long long row, long long col, float v) {
   v *= p.alpha;
   if (p.bias) v += p.bias_f32 ? static_cast<const float*>(p.bias)[col] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col]);
-  if (p.aux_out) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(v);
-  if (p.act >= 1 && p.act <= 4) v = act_fwd(p.act, v);
+  if (p.aux_out) p.aux_out[row * p.ld_aux_out + col] = __float2bfloat16(aux_value(p.act, v));
+  if (p.act >= 1 && p.act <= 5) v = act_fwd(p.act, v);
   if (p.act >= 11) v *= act_bwd(p.act, __bfloat162float(p.aux_in[row * p.ld_aux_in + col]));
   if (p.residual) v += __bfloat162float(p.residual[row * p.ldr + col]);
   if (p.out_f32) {
@@ -205,6 +210,7 @@ __device__ __forceinline__ void apply_act8(int act, float (&v)[8]) {
       for (int i = 0; i < 8; ++i) v[i] = fmaxf(v[i], 0.0f);
       break;
     case 2:
+    case 5:
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float x = v[i];
@@ -251,8 +257,16 @@ __device__ __forceinline__ void apply_act_bwd8(int act, float (&v)[8], const flo
         v[i] *= sg * (1.0f + x[i] * (1.0f - sg));
       }
       break;
+    case 15:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= x[i];
+      break;
     default: break;
   }
+}
+__device__ __forceinline__ void aux_value8(int act, const float (&v)[8], float (&o)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = aux_value(act, v[i]);
 }
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
@@ -295,8 +309,12 @@ __device__ __forceinline__ void epilogue_phase2(const GemmParams& p, const uint8
       for (int e = 0; e < 8; ++e) v[e] += bias8[e];
     }
     if (full) {
-      if (p.aux_out) *reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col) = pack8(v);
-      if (p.act >= 1 && p.act <= 4) apply_act8(p.act, v);
+      if (p.aux_out) {
+        float av[8];
+        aux_value8(p.act, v, av);
+        *reinterpret_cast<uint4*>(p.aux_out + row * p.ld_aux_out + col) = pack8(av);
+      }
+      if (p.act >= 1 && p.act <= 5) apply_act8(p.act, v);
       if (p.act >= 11) {
         float x[8];
         unpack8(*reinterpret_cast<const uint4*>(p.aux_in + row * p.ld_aux_in + col), x);
@@ -320,10 +338,10 @@ __device__ __forceinline__ void epilogue_phase2(const GemmParams& p, const uint8
 #pragma unroll
       for (int e = 0; e < 8; ++e)
         if (col + e < p.N) {
-          if (p.aux_out) p.aux_out[row * p.ld_aux_out + col + e] = __float2bfloat16(v[e]);
+          if (p.aux_out) p.aux_out[row * p.ld_aux_out + col + e] = __float2bfloat16(aux_value(p.act, v[e]));
           if (p.act >= 11) x[e] = __bfloat162float(p.aux_in[row * p.ld_aux_in + col + e]);
         }
-      if (p.act >= 1 && p.act <= 4) apply_act8(p.act, v);
+      if (p.act >= 1 && p.act <= 5) apply_act8(p.act, v);
       if (p.act >= 11) apply_act_bwd8(p.act, v, x);
 #pragma unroll
       for (int e = 0; e < 8; ++e)
@@ -352,11 +370,11 @@ __device__ __forceinline__ void epilogue_direct_f32(const GemmParams& p, long lo
       if (c < p.N) {
         if (p.bias) v[e] += p.bias_f32 ? __ldg(static_cast<const float*>(p.bias) + c)
                                        : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[c]);
-        if (p.aux_out) p.aux_out[row * p.ld_aux_out + c] = __float2bfloat16(v[e]);
+        if (p.aux_out) p.aux_out[row * p.ld_aux_out + c] = __float2bfloat16(aux_value(p.act, v[e]));
         if (p.act >= 11) x[e] = __bfloat162float(p.aux_in[row * p.ld_aux_in + c]);
       }
     }
-    if (p.act >= 1 && p.act <= 4) apply_act8(p.act, v);
+    if (p.act >= 1 && p.act <= 5) apply_act8(p.act, v);
     if (p.act >= 11) apply_act_bwd8(p.act, v, x);
     if (full) {
 #pragma unroll
@@ -501,10 +519,14 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
   if (p.aux_out) {
     uint4 o[8];
 #pragma unroll
-    for (int g = 0; g < 8; ++g) o[g] = pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
+    for (int g = 0; g < 8; ++g) {
+      float av[8];
+      aux_value8(p.act, reinterpret_cast<const float(&)[8]>(v[g * 8]), av);
+      o[g] = pack8(av);
+    }
     if (live) st_row64(p.aux_out + row * p.ld_aux_out + col0, wide, o);
   }
-  if (p.act == 2) {
+  if (p.act == 2 || p.act == 5) {
     // GELU (tanh form), the one activation on the training hot path, outside the per-group dispatch: five
     // multiply-adds and one tanh.approx per element, all 64 elements independent.
 #pragma unroll
@@ -514,7 +536,7 @@ __device__ __forceinline__ void epi_finish_row(const GemmParams& p, const uint32
       const float hx = 0.5f * x;
       v[i] = fmaf(hx, tanh_fast(u), hx);
     }
-  } else if (p.act >= 1 && p.act <= 4) {
+  } else if (p.act >= 1 && p.act <= 5) {
 #pragma unroll
     for (int g = 0; g < 8; ++g) apply_act8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]));
   }
@@ -593,13 +615,38 @@ __device__ __forceinline__ void epi_half_tma(const GemmParams& p, const uint32_t
   }
   uint8_t* row_aux = buf_aux + lane * 128;
   uint8_t* row_c = buf_c + lane * 128;
-  if (p.aux_out) {
+  if (p.aux_out && p.act != 5) {
 #pragma unroll
     for (int g = 0; g < 4; ++g)
       *reinterpret_cast<uint4*>(row_aux + (((h * 4 + g) ^ (lane & 7)) << 4)) =
           pack8(reinterpret_cast<const float(&)[8]>(v[g * 8]));
   }
-  if (p.act == 2) {
+  if (p.act == 5) {
+    // GELU and its derivative from one tanh, on pairs of values; the derivative goes to the auxiliary block:
+    //   y = x (0.5 + 0.5 t),  d = 0.5 + 0.5 (t + x (c0 + c2 x^2) (1 - t^2)),  t = tanh(x (c0 + c1 x^2))
+    const f32x2 c0 = f2_splat(0.7978845608f), c1 = f2_splat(0.0356774081f), c2 = f2_splat(0.1070322243f);
+    const f32x2 one = f2_splat(1.0f), hf = f2_splat(0.5f);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      float d[8];
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const int i = g * 8 + e;
+        const f32x2 x = f2_pack(v[i], v[i + 1]);
+        const f32x2 xx = f2_mul(x, x);
+        float u0, u1;
+        f2_unpack(f2_mul(x, f2_fma(xx, c1, c0)), u0, u1);
+        const float t0 = tanh_fast(u0), t1 = tanh_fast(u1);
+        const f32x2 t = f2_pack(t0, t1), nt = f2_pack(-t0, -t1);
+        const f32x2 hx = f2_mul(x, hf);
+        const f32x2 sl = f2_mul(x, f2_fma(xx, c2, c0));
+        const f32x2 w = f2_fma(sl, f2_fma(nt, t, one), t);
+        f2_unpack(f2_fma(w, hf, hf), d[e], d[e + 1]);
+        f2_unpack(f2_fma(hx, t, hx), v[i], v[i + 1]);
+      }
+      *reinterpret_cast<uint4*>(row_aux + (((h * 4 + g) ^ (lane & 7)) << 4)) = pack8(d);
+    }
+  } else if (p.act == 2) {
     // GELU (tanh form) on pairs of values: x * (0.5 + 0.5 tanh(x (c0 + c1 x^2)))
     const f32x2 c0 = f2_splat(0.7978845608f), c1 = f2_splat(0.0356774081f), hf = f2_splat(0.5f);
 #pragma unroll
@@ -612,7 +659,7 @@ __device__ __forceinline__ void epi_half_tma(const GemmParams& p, const uint32_t
       const f32x2 hx = f2_mul(x, hf);
       f2_unpack(f2_fma(hx, t, hx), v[i], v[i + 1]);
     }
-  } else if (p.act >= 1 && p.act <= 4) {
+  } else if (p.act >= 1 && p.act <= 5) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) apply_act8(p.act, reinterpret_cast<float(&)[8]>(v[g * 8]));
   }
@@ -622,7 +669,10 @@ __device__ __forceinline__ void epi_half_tma(const GemmParams& p, const uint32_t
       float x[8];
       unpack8(*reinterpret_cast<const uint4*>(row_c + (((h * 4 + g) ^ (lane & 7)) << 4)), x);
       if (in_kind == 1) {
-        if (p.act == 12) {
+        if (p.act == 15) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[g * 8 + e] *= x[e];
+        } else if (p.act == 12) {
           // GELU' on pairs: 0.5 (1 + t) + 0.5 x (1 - t^2) (c0 + c2 x^2),  t = tanh(x (c0 + c1 x^2))
           const f32x2 c0 = f2_splat(0.7978845608f), c1 = f2_splat(0.0356774081f), c2 = f2_splat(0.1070322243f);
           const f32x2 one = f2_splat(1.0f), hf = f2_splat(0.5f);
@@ -755,8 +805,8 @@ struct GemmSmem {
   static constexpr int kStageOff = STAGES * (kABytes + kBBytes);   // epilogue staging
   static constexpr int kBiasOff = kStageOff + kEpiWarps * kStagePerWarp;   // 64 bf16 bias values per epilogue warp
   static constexpr int kBarOffset = kBiasOff + kEpiWarps * 128;
-  // barriers: full / empty per stage, 2 + 2 accumulator, 1 drain, 1 epilogue-input per epilogue warp
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1 + kEpiWarps) * 8 + 32 + 1024;  // + alignment slack
+  // barriers: full / empty per stage, 2 + 2 accumulator, 1 drain, 2 epilogue-input per epilogue warp
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4 + 1 + 2 * kEpiWarps) * 8 + 32 + 1024;  // + alignment slack
   static_assert(kTotal <= 227 * 1024, "GEMM: shared memory budget");
 };
 
@@ -787,8 +837,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* drain_bar = tmem_empty + 2;
-  uint64_t* epi_in_bar = drain_bar + 1;            // [kEpiWarps]: input block of the tile-store epilogue has landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_in_bar + kEpiWarps);
+  uint64_t* epi_in_bar = drain_bar + 1;            // [kEpiWarps][2]: an input block of the tile-store epilogue has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_in_bar + 2 * kEpiWarps);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* epi_ctr = reinterpret_cast<int*>(tmem_slot + 2);       // arrival counter of the epilogue-warp barrier
   volatile int* epi_last = reinterpret_cast<volatile int*>(tmem_slot + 3);
@@ -824,7 +874,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         mbar_init(&tmem_empty[a], PAIR ? 2 * kEpiWarps : kEpiWarps);   // the leader's is released by both CTAs
       }
       mbar_init(drain_bar, 1);
-      for (int w = 0; w < kEpiWarps; ++w) mbar_init(&epi_in_bar[w], 1);
+      for (int w = 0; w < 2 * kEpiWarps; ++w) mbar_init(&epi_in_bar[w], 1);
       mbar_fence_init();
     }
     __syncwarp();
@@ -1013,7 +1063,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* stage = smem + L::kStageOff + ew * L::kStagePerWarp;
     uint32_t local_tile = 0;
     uint32_t epi_blk = 0;        // blocks this warp has stored through the tile-store epilogue
-    uint32_t epi_in_ph = 0;      // phase of this warp's input barrier
+    uint32_t epi_in_ph = 0;      // phases of this warp's two input barriers (bit j: staging block j)
+    uint32_t epi_in_pf = 0;      // bit j: the input of the coming tile's block j has been requested already
     int epi_gen = 0;
     // Registers of one 64-column chunk of this thread's row -> final epilogue (staged bf16 path or direct fp32 path).
     auto emit = [&](long long row0, long long col0, const uint32_t (&r0)[32], const uint32_t (&r1)[32]) {
@@ -1109,9 +1160,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int n0 = ni * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
-      // Tile-store epilogue: this warp's bias slices are requested before the wait for the accumulator.
-      // and the per-element input blocks (residual / activation input / C) are fetched into the staging blocks by tile
-      // loads, so that neither latency is paid after the accumulator has arrived.
+      // Tile-store epilogue: this warp's bias slices are requested before the wait for the accumulator, and the
+      // per-element input blocks (residual / saved activation derivative / C) are fetched into the staging blocks by
+      // tile loads one block of work ahead: block 0 of a tile while block 1 of the tile before it is worked on, block 1
+      // here, while block 0 is worked on.  Neither latency is paid after the accumulator has arrived.
       uint32_t bias_pf[BN / 128] = {};
       const int epi_in_kind = p.act >= 11 ? 1 : (p.residual ? 2 : (p.accumulate ? 3 : 0));
       if constexpr (PAIR) {
@@ -1124,18 +1176,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 bias_pf[j] = __ldg(reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(p.bias) + col));
             }
           }
-          if (epi_in_kind && lane == 0) {
-            int nblk = 0;
-#pragma unroll
-            for (int j = 0; j < BN / 128; ++j) nblk += ((long long)n0 + (half + 2 * j) * 64 < p.N) ? 1 : 0;
-            if (nblk > 0) {
-              bulk_wait_read_all();   // the previous tile's stores have finished reading both staging blocks
-              mbar_arrive_expect_tx(&epi_in_bar[ew], 4096u * nblk);
-              for (int j = 0; j < nblk; ++j)
-                tma_load_2d(stage + j * 4096, &em.in, &epi_in_bar[ew], n0 + (half + 2 * j) * 64, m0 + q * 32);
+          if (epi_in_kind) {
+            // Block 0 when it was not requested during the previous tile (the first tile of this CTA, or one that
+            // follows a tile without rows): wait until the stores have finished reading the staging block, then load.
+            if (!(epi_in_pf & 1u) && (long long)n0 + half * 64 < p.N && lane == 0) {
+              bulk_wait_read_all();
+              mbar_arrive_expect_tx(&epi_in_bar[ew * 2], 4096u);
+              tma_load_2d(stage, &em.in, &epi_in_bar[ew * 2], n0 + half * 64, m0 + q * 32);
             }
           }
         }
+        epi_in_pf = 0;
       }
       DPTB_PROF_BEGIN(prof_t0);
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full[acc], acc_ph, abort_flag, kWaitTmemFullTimeout))) break;
@@ -1215,9 +1266,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (p.aux_out) bulk_wait_read_all();
             else bulk_wait_read_1();
           }
-          if (in_kind && j == 0) {   // one barrier phase per tile covers both input blocks
-            ok = __all_sync(0xffffffffu, mbar_wait(&epi_in_bar[ew], epi_in_ph, abort_flag, kWaitFullTimeout));
-            epi_in_ph ^= 1;
+          if (in_kind) {
+            if (BN / 128 > 1 && j == 0 && col0 + 128 < p.N) {
+              // Block 1's input, while the accumulator load above is in flight: its staging block was handed to a
+              // store at the end of the previous tile, which has had the accumulator wait to finish reading it.
+              if (lane == 0) {
+                bulk_wait_read_all();
+                mbar_arrive_expect_tx(&epi_in_bar[ew * 2 + 1], 4096u);
+                tma_load_2d(stage + 4096, &em.in, &epi_in_bar[ew * 2 + 1], (int)col0 + 128, (int)row0);
+              }
+            }
+            if (BN / 128 > 1 && j == BN / 128 - 1 && unit + unit_step < num_units) {
+              // The first block of the NEXT tile is requested now, a block's worth of work before it is needed: its
+              // staging block is free once this tile's first store has finished reading it.
+              const int ns = (unit + unit_step) % num_tiles;
+              const int nmi = (ns % sched_tiles_m) * 2 + (int)cta_rank;
+              const int nx_m0 = nmi * kBM, nx_n0 = (ns / sched_tiles_m) * BN;
+              if (nmi < p.tiles_m && (long long)nx_m0 + q * 32 < p.M && (long long)nx_n0 + half * 64 < p.N) {
+                if (lane == 0) {
+                  bulk_wait_read_all();
+                  mbar_arrive_expect_tx(&epi_in_bar[ew * 2], 4096u);
+                  tma_load_2d(stage, &em.in, &epi_in_bar[ew * 2], nx_n0 + half * 64, nx_m0 + q * 32);
+                }
+                epi_in_pf |= 1u;
+              }
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(&epi_in_bar[ew * 2 + j], (epi_in_ph >> j) & 1u, abort_flag,
+                                                   kWaitFullTimeout));
+            epi_in_ph ^= 1u << j;
           }
           tmem_ld_wait();
           __syncwarp();              // bias slice and buffer release are visible to every lane
@@ -1540,6 +1616,7 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
   p.aux_in = static_cast<const __nv_bfloat16*>(a->aux_in); p.ld_aux_in = a->ld_aux_in;
   p.act = a->act; p.out_f32 = a->out_f32; p.accumulate = a->accumulate; p.alpha = a->alpha;
   if (p.act >= 11 && !p.aux_in) return kErrBadShape;
+  if (p.act == 5 && !p.aux_out) p.act = 2;
 
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   const bool tc_ok = !a->force_simt && !a->a_f32 && !a->b_f32 && a->K > 0 && al16(a_ptr) && al16(a->B) &&

@@ -133,9 +133,12 @@ class MLPFn(torch.autograd.Function):
     def forward(ctx, x, w1, b1, w2, b2, act, residual):
         x2 = _as2d(x)
         M, F, D = x2.shape[0], w1.shape[0], w2.shape[0]
+        # For GELU the saved tensor is the derivative at the pre-activation (computed beside the activation from the
+        # same tanh), so the backward epilogue is one multiply; other activations save the pre-activation itself.
         pre = torch.empty(M, F, dtype=x.dtype, device=x.device)
         a = torch.empty_like(pre)
-        K.gemm(x2, w1, a, trans_b=True, bias=None if b1 is None else b1.view(-1), act=act, aux_out=pre)
+        fwd_act = "gelu_tanh_d" if act == "gelu_tanh" else act
+        K.gemm(x2, w1, a, trans_b=True, bias=None if b1 is None else b1.view(-1), act=fwd_act, aux_out=pre)
         out = torch.empty(M, D, dtype=x.dtype, device=x.device)
         K.gemm(a, w2, out, trans_b=True, bias=None if b2 is None else b2.view(-1),
                residual=None if residual is None else _as2d(residual))
@@ -152,7 +155,7 @@ class MLPFn(torch.autograd.Function):
         w1, b1, w2, b2 = ctx.params
         dy2 = _as2d(dy)
         dpre = torch.empty_like(pre)
-        K.gemm(dy2, w2, dpre, aux_in=pre, act_bwd=ctx.act)
+        K.gemm(dy2, w2, dpre, aux_in=pre, act_bwd="mul" if ctx.act == "gelu_tanh" else ctx.act)
         dw2 = _weight_grad(dy2, a, w2, ctx.needs_input_grad[3])
         db2 = _bias_grad(dy2, b2, ctx.needs_input_grad[4])
         dw1 = _weight_grad(dpre, x2, w1, ctx.needs_input_grad[1])

@@ -13,8 +13,10 @@ import torch
 
 from .. import _native as N
 
-ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu_tanh": 2, "quick_gelu": 3, "silu": 4}
-ACT_BWD_CODES = {"relu": 11, "gelu_tanh": 12, "quick_gelu": 13, "silu": 14}
+# "gelu_tanh_d" applies the same GELU but writes the activation's derivative (not the pre-activation) to ``aux_out``;
+# the matching backward code "mul" multiplies by ``aux_in`` as it is.  One tanh per element instead of two per step.
+ACT_CODES = {None: 0, "none": 0, "relu": 1, "gelu_tanh": 2, "quick_gelu": 3, "silu": 4, "gelu_tanh_d": 5}
+ACT_BWD_CODES = {"relu": 11, "gelu_tanh": 12, "quick_gelu": 13, "silu": 14, "mul": 15}
 
 
 def _lead(t: torch.Tensor) -> int:
@@ -54,7 +56,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, trans_a: bool =
     ``a`` is stored ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is stored ``[K,N]`` (or ``[N,K]`` with ``trans_b``,
     the layout of an ``nn.Linear`` weight).  All operands are 2-D with a contiguous last axis; row strides may exceed
     the row length (padded buffers).  ``n_cols`` restricts N below ``out.shape[1]``.
-    Epilogue order: ``*alpha, +bias, aux_out<-value, act, *act'(aux_in), +residual, (+out)``.
+    Epilogue order: ``*alpha, +bias, aux_out<-value (or act'(value) with "gelu_tanh_d"), act, *act'(aux_in), +residual,
+    (+out)``.
     """
     lib = N.load()
     if trans_a:

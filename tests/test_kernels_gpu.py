@@ -126,6 +126,24 @@ def test_gemm_epilogue_act_backward(act):
     assert _rel_err(out, x.grad) < 2e-2
 
 
+@pytest.mark.parametrize("M,N,Kd", [(256, 256, 128), (512, 3072, 768), (100, 200, 72)])
+def test_gemm_gelu_with_saved_derivative(M, N, Kd):
+    """Forward GELU that saves the derivative instead of the pre-activation, and the one-multiply backward epilogue."""
+    x, w, b = _mk((M, Kd), seed=41), _mk((N, Kd), scale=0.05, seed=42), _mk((N,), seed=43)
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    d = torch.empty_like(y)
+    K.gemm(x, w, y, trans_b=True, bias=b, act="gelu_tanh_d", aux_out=d)
+    pre = (x.float() @ w.float().t() + b.float()).requires_grad_(True)
+    ref = R.ACTIVATIONS["gelu_tanh"](pre)
+    ref.sum().backward()
+    assert _rel_err(y, ref) < 1e-2
+    assert _rel_err(d, pre.grad) < 1e-2
+    dy, w2 = _mk((M, Kd), seed=44), _mk((Kd, N), scale=0.05, seed=45)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.gemm(dy, w2, out, aux_in=d, act_bwd="mul")
+    assert _rel_err(out, (dy.float() @ w2.float()) * d.float()) < 1e-2
+
+
 def test_gemm_accumulate_fp32_out_and_padded_ld():
     M, N, Kd = 256, 200, 128
     a, w = _mk((M, Kd), seed=10), _mk((N, Kd), seed=11)
