@@ -7,7 +7,7 @@ Every path is one kernel of this package that does its arithmetic and moves its 
 
   P1   data-parallel gradient all-reduce (+ sum of squares for the clip), per bucket     csrc/dp_allreduce.cu
   P2a  row-parallel GEMM + all-reduce / + reduce-scatter (prefill and decode rows)        csrc/gemm.cu, gemm_skinny.cu
-  P2b  all-gather + column-parallel GEMM                                                  csrc/gemm.cu
+  P2b  all-gather + column-parallel GEMM (shards staged by copies / read in place)        parallel/tp.py, csrc/gemm.cu
   P3   expert-parallel MoE layer forward: route, dispatch, expert SwiGLU GEMMs, combine   csrc/moe_ep.cu
 
 Each is timed with CUDA events on the launching stream after warm-up, a barrier and a synchronise on both sides, and
@@ -178,12 +178,15 @@ def main():
                 out = torch.empty(M, Nn, **bf)
                 comm.buffer(1, rows_per).normal_()
 
-                def run():
-                    comm.publish_shard()
-                    comm.allgather_gemm(1, rows_per, w, out)
-                ms = timed(run, group)
-                add("P2b", f"all-gather + GEMM {name}: [{M},{D}] (sharded by rows) x [{Nn},{D}]^T", ms, 2.0 * M * D * Nn,
-                    2.0 * M * D * (world - 1) / world, link_bw, "peers' row shards read in place by the GEMM's tile loads")
+                for staged in (True, False):
+                    def run():
+                        comm.publish_shard()
+                        comm.allgather_gemm(1, rows_per, w, out, staged=staged)
+                    ms = timed(run, group)
+                    how = ("peer shards copied once into local memory on a side stream, GEMM per shard" if staged else
+                           "one kernel: peers' row shards read in place by the GEMM's tile loads")
+                    add("P2b", f"all-gather + GEMM {name} ({'staged' if staged else 'in place'}): [{M},{D}] (sharded by "
+                        f"rows) x [{Nn},{D}]^T", ms, 2.0 * M * D * Nn, 2.0 * M * D * (world - 1) / world, link_bw, how)
         _native.raise_on_device_error()
         del comm
 

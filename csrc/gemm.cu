@@ -1858,6 +1858,31 @@ extern "C" int dptb_tp_signal(const DptbTpSignalArgs* a, void* stream_v) {
   return counted(1, (int)cudaGetLastError());
 }
 
+// Stream-ordered wait for the peers' shards: returns once every other rank's "shard ready" flag in THIS rank's flag
+// array has reached this rank's own publication count (so it runs after this rank's dptb_tp_signal).  Each wait is
+// bounded; one that runs out is recorded in the status word and the kernel returns all the same.  What follows it on
+// the stream (copies of the peers' shards into local memory) then sees complete shards.
+namespace dptb {
+__global__ void tp_wait_ready_kernel(const uint32_t* ready, const uint32_t* epoch, int world, int rank) {
+  const uint32_t e = *reinterpret_cast<const volatile uint32_t*>(epoch);
+  const int src = threadIdx.x;
+  if (src < world && src != rank) wait_flag_ge(ready + src, e);
+}
+}  // namespace dptb
+// One device-to-device copy on the stream by the copy engines (no SM is taken from the GEMM that runs beside it);
+// either pointer may be peer-mapped memory.
+extern "C" int dptb_copy_async(void* dst, const void* src, long long nbytes, void* stream_v) {
+  if (nbytes <= 0) return 0;
+  if (!dst || !src) return kErrBadShape;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)nbytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream_v));
+}
+extern "C" int dptb_tp_wait_ready(const void* ready, const void* epoch, int world, int rank, void* stream_v) {
+  if (!ready || !epoch || world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return kErrBadShape;
+  tp_wait_ready_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_v)>>>(
+      static_cast<const uint32_t*>(ready), static_cast<const uint32_t*>(epoch), world, rank);
+  return counted(1, (int)cudaGetLastError());
+}
+
 // Status word access ------------------------------------------------------------------------------
 // Folds the blocks of all translation units: the first non-zero code (with its detail) and the total number of
 // waits that ran out.

@@ -60,6 +60,10 @@ def _declare(lib):
     lib.dptb_allgather_gemm.restype = c_int
     lib.dptb_tp_signal.argtypes = [ctypes.POINTER(TpSignalArgs), c_void_p]
     lib.dptb_tp_signal.restype = c_int
+    lib.dptb_tp_wait_ready.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.dptb_tp_wait_ready.restype = c_int
+    lib.dptb_copy_async.argtypes = [c_void_p, c_void_p, c_ll, c_void_p]
+    lib.dptb_copy_async.restype = c_int
     lib.dptb_gemm_skinny.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpArArgs), c_void_p]
     lib.dptb_gemm_skinny.restype = c_int
     lib.dptb_gemm_skinny_oneshot.argtypes = [ctypes.POINTER(N.GemmArgs), ctypes.POINTER(TpOneShotArgs), c_void_p]
@@ -114,6 +118,7 @@ class TpComm:
         self.ready.zero_()
         self._h_ready = symm_mem.rendezvous(self.ready, group=gname)
         self.ag_epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._ag_side, self._ag_events, self._ag_stage = None, None, None   # staged all-gather GEMM (made on first use)
         mc_ok = all(int(getattr(h, "multicast_ptr", 0) or 0) != 0 for h in [self._h_partial] + self._h_bufs)
         want = mc_ok if use_nvls is None else use_nvls
         env = os.environ.get("DPTB200_TP_NVLS")
@@ -245,23 +250,32 @@ class TpComm:
         N.check(self.lib.dptb_tp_signal(ctypes.byref(self._sig), N.stream_ptr()), "tp_signal")
 
     def allgather_gemm(self, in_index: int, rows_per_rank: int, w_shard: torch.Tensor, out: torch.Tensor,
-                       bias: Optional[torch.Tensor] = None, act=None) -> torch.Tensor:
+                       bias: Optional[torch.Tensor] = None, act=None, staged: Optional[bool] = None) -> torch.Tensor:
         """``out[world * rows_per_rank, N] = concat_over_ranks(shard_r) @ w_shard^T``: column-parallel Linear whose
         input is row-sharded.  Rank r's shard is the first ``rows_per_rank`` rows of ITS activation buffer
-        ``in_index``; the kernel reads the peers' shards in place over NVLink (``publish_shard`` first)."""
+        ``in_index`` (``publish_shard`` first).
+
+        ``staged`` (the default; ``DPTB200_TP_AG_STAGED=0`` turns it off): every peer shard crosses NVLink once, copied
+        into local memory on a side stream while the GEMM of the shard before it runs, own shard first.  Otherwise one
+        kernel reads the peers' shards in place with its tile loads, which moves every remote tile once per column
+        tile of the output (measured 4-5 times slower at the Llama-3-8B shapes)."""
         if rows_per_rank % 128 or rows_per_rank > self.max_rows:
             raise ValueError("allgather_gemm: rows_per_rank must be a multiple of 128 within the buffer")
-        Nn, K = w_shard.shape
-        if K != self.width:
-            raise ValueError(f"allgather_gemm: inner dimension {K} != buffer width {self.width}")
+        Nn, Kd = w_shard.shape
+        if Kd != self.width:
+            raise ValueError(f"allgather_gemm: inner dimension {Kd} != buffer width {self.width}")
         M = rows_per_rank * self.world
         if out.shape[0] != M or out.shape[1] < Nn or out.dtype != torch.bfloat16 or out.stride(-1) != 1:
             raise ValueError("allgather_gemm: output must be bf16 [world * rows_per_rank, >= N]")
+        if staged is None:
+            staged = os.environ.get("DPTB200_TP_AG_STAGED", "1") != "0"
+        if staged and self.world > 1:
+            return self._allgather_gemm_staged(in_index, rows_per_rank, w_shard, out, bias, act)
         g = N.GemmArgs()
         src = self.bufs[in_index]
         g.A, g.B, g.C = src.data_ptr(), w_shard.data_ptr(), out.data_ptr()
         g.lda, g.ldb, g.ldc = src.stride(0), w_shard.stride(0), out.stride(0)
-        g.M, g.N, g.K = M, Nn, K
+        g.M, g.N, g.K = M, Nn, Kd
         g.trans_a, g.trans_b = 0, 1
         g.alpha, g.splits = 1.0, 1
         if bias is not None:
@@ -274,6 +288,38 @@ class TpComm:
             ag.a_peer[r] = int(self._h_bufs[in_index].buffer_ptrs[r]) if r < self.world else None
         ag.ready, ag.epoch = self.ready.data_ptr(), self.ag_epoch.data_ptr()
         N.check(self.lib.dptb_allgather_gemm(ctypes.byref(g), ctypes.byref(ag), N.stream_ptr()), "allgather_gemm")
+        return out
+
+    def _allgather_gemm_staged(self, in_index, rows, w_shard, out, bias, act):
+        """Gather by copy, GEMM by shard: the side stream waits (bounded, on the device) for the peers' "shard ready"
+        flags, then copies shard after shard into a local staging matrix; the launching stream multiplies this rank's
+        own shard at once and each staged shard as soon as its copy has finished."""
+        if self._ag_side is None:
+            self._ag_side = torch.cuda.Stream(device=self.device)
+            self._ag_events = [torch.cuda.Event() for _ in range(self.world + 1)]
+        need = self.world * rows
+        if self._ag_stage is None or self._ag_stage.shape[0] < need:
+            self._ag_stage = torch.empty(need, self.width, dtype=torch.bfloat16, device=self.device)
+        stage, side, evs = self._ag_stage, self._ag_side, self._ag_events
+        main = torch.cuda.current_stream(self.device)
+        order = [(self.rank + i) % self.world for i in range(1, self.world)]
+        evs[self.world].record(main)          # after publish_shard, and after the previous consumers of the staging rows
+        with torch.cuda.stream(side):
+            side.wait_event(evs[self.world])
+            N.check(self.lib.dptb_tp_wait_ready(self.ready.data_ptr(), self.ag_epoch.data_ptr(), self.world, self.rank,
+                                                N.stream_ptr()), "tp_wait_ready")
+            for s in order:
+                N.check(self.lib.dptb_copy_async(stage[s * rows:(s + 1) * rows].data_ptr(),
+                                                 int(self._h_bufs[in_index].buffer_ptrs[s]),
+                                                 rows * self.width * 2, N.stream_ptr()), "copy_async")
+                evs[s].record(side)
+        b = None if bias is None else bias.view(-1)
+        K.gemm(self.bufs[in_index][:rows], w_shard, out[self.rank * rows:(self.rank + 1) * rows], trans_b=True, bias=b,
+               act=act, n_cols=w_shard.shape[0])
+        for s in order:
+            main.wait_event(evs[s])
+            K.gemm(stage[s * rows:(s + 1) * rows], w_shard, out[s * rows:(s + 1) * rows], trans_b=True, bias=b, act=act,
+                   n_cols=w_shard.shape[0])
         return out
 
 

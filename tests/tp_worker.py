@@ -61,11 +61,14 @@ def check_sequence_parallel(comm, rank, world, tag):
         x, w1s = x_full[:, lo:hi].contiguous(), w1[:, lo:hi].contiguous()
         w2s, b2s = w2[n_lo:n_hi].contiguous(), bias2[n_lo:n_hi].contiguous()
         res_shard = res[rank * rows_per_rank:(rank + 1) * rows_per_rank].contiguous()
-        out = torch.empty(M, n_hi - n_lo, dtype=torch.bfloat16, device="cuda")
-        for rep in range(3):
+        # both forms of the all-gather GEMM, alternating: peers' shards staged in local memory by copies on a side
+        # stream, and read in place by the GEMM kernel's own tile loads
+        outs = {True: torch.empty(M, n_hi - n_lo, dtype=torch.bfloat16, device="cuda"),
+                False: torch.empty(M, n_hi - n_lo, dtype=torch.bfloat16, device="cuda")}
+        for rep in range(4):
             shard = comm.gemm_reduce_scatter(x, w1s, 0, residual=res_shard)
             comm.publish_shard()
-            comm.allgather_gemm(0, rows_per_rank, w2s, out, bias=b2s)
+            comm.allgather_gemm(0, rows_per_rank, w2s, outs[rep % 2 == 0], bias=b2s, staged=(rep % 2 == 0))
             # the next reduce-scatter overwrites buffer 0: its end barrier orders it after every rank's all-gather
         torch.cuda.synchronize()
         _native.raise_on_device_error()
@@ -73,8 +76,10 @@ def check_sequence_parallel(comm, rank, world, tag):
         err = (shard.float() - mid[rank * rows_per_rank:(rank + 1) * rows_per_rank]).abs().max().item()
         assert err <= 0.02 * mid.abs().max().item() + 0.05, f"{tag} reduce-scatter rows/rank={rows_per_rank}: err {err}"
         want = (mid.bfloat16().float() @ w2.float().t() + bias2.float())[:, n_lo:n_hi]
-        err = (out.float() - want).abs().max().item()
-        assert err <= 0.03 * want.abs().max().item() + 0.05, f"{tag} all-gather GEMM rows/rank={rows_per_rank}: err {err}"
+        for staged, out in outs.items():
+            err = (out.float() - want).abs().max().item()
+            assert err <= 0.03 * want.abs().max().item() + 0.05, \
+                f"{tag} all-gather GEMM (staged={staged}) rows/rank={rows_per_rank}: err {err}"
     if rank == 0:
         print(f"tp_worker {tag}: reduce-scatter GEMM and all-gather GEMM match")
 
