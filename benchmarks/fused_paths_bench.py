@@ -125,9 +125,11 @@ def main():
                 red.finalize(ctrl, 1.0)
             ms = timed(run, group)
             B = 2 * n
-            # multimem: this GPU's port carries its reduced slice in and its slices of the peers' reads out, then the
-            # broadcast both ways: about one bucket per direction; peer loads / stores: 2 (N-1)/N buckets per direction
-            link_bytes = B if red.use_nvls else 2.0 * B * (world - 1) / world
+            # multimem: the switch reads every member's copy of a slice, the requester's own included, so a port sends
+            # the whole bucket out while its reduced slice (1/N) comes in, and the broadcast is the mirror image:
+            # (1 + 1/N) buckets per direction (the N / (N + 1) bus-bandwidth factor of in-switch all-reduce);
+            # peer loads / stores: 2 (N-1)/N buckets per direction
+            link_bytes = B * (1.0 + 1.0 / world) if red.use_nvls else 2.0 * B * (world - 1) / world
             add("P1", f"dp_allreduce bucket {mb} MiB ({'multimem' if red.use_nvls else 'peer ld/st'})", ms, 0.0,
                 link_bytes, link_bw)
             del red, arena
@@ -150,15 +152,21 @@ def main():
             out_bytes = 2.0 * M * D
             flops = 2.0 * M * D * Kr
             if on("p2a"):
+                # through the switch (multimem) a port carries (1 + 1/N) outputs per direction for the all-reduce and one
+                # output for the reduce-scatter (every member's partial is read, the owner's included); over peer
+                # pointers (N-1)/N of an output per phase
+                nv = bool(comm.use_nvls)
+                ar_bytes = out_bytes * (1.0 + 1.0 / world) if nv else 2.0 * out_bytes * (world - 1) / world
+                rs_bytes = out_bytes if nv else out_bytes * (world - 1) / world
                 ms = timed(lambda: comm.gemm_allreduce(x, w, 0, residual=res), group)
-                add("P2a", f"GEMM + all-reduce, prefill {name}: [{M},{Kr}] x [{D},{Kr}]^T", ms, flops, out_bytes, link_bw,
-                    "owner gathers the partial tile (in), broadcasts the sum (out): ~1 output per direction")
+                add("P2a", f"GEMM + all-reduce, prefill {name}: [{M},{Kr}] x [{D},{Kr}]^T", ms, flops, ar_bytes, link_bw,
+                    "owner reduces the partial tile through the switch, broadcasts the sum")
                 if M % (world * 128) == 0:
                     rs_res = comm.buffer(2, M // world)
                     rs_res.normal_()
                     ms = timed(lambda: comm.gemm_reduce_scatter(x, w, 0, residual=rs_res), group)
                     add("P2a", f"GEMM + reduce-scatter, prefill {name}: [{M},{Kr}] x [{D},{Kr}]^T", ms, flops,
-                        out_bytes * (world - 1) / world, link_bw)
+                        rs_bytes, link_bw)
                 xs, ress = x[:32].contiguous(), comm.buffer(1, 32)
                 ms = timed(lambda: comm.gemm_allreduce(xs, w, 0, residual=ress), group, iters=20)
                 # decode rows: the floor is streaming this rank's weight slice from HBM, not NVLink
