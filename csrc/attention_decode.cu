@@ -8,15 +8,19 @@
 // attention streams each KV row exactly once for all query heads that share it (grouped-query attention).
 //
 // attn_decode_kernel: grid (splits, Hkv, B * Sq).  A CTA owns one (sequence, query position, kv head) and a contiguous
-// chunk of the keys; its 4 warps take 32-key blocks round-robin.  A key / value row is read by hd/8 lanes with one
-// 16-byte load each (several keys per load instruction, eight loads in flight per lane), scores of the G = Hq / Hkv
-// grouped heads are reduced with shuffles inside those lanes, the softmax is computed per 32-key block (lane j owns
-// key j) and the block's probabilities are fetched back by shuffle for the P.V accumulation.  Partial (max, sum, acc) per (warp -> CTA -> split) are
-// merged in shared memory and, when the keys are split across CTAs, through an fp32 workspace by attn_decode_merge.
+// chunk of the keys; its 4 warps take 16-key rounds round-robin, each through a private two-stage cp.async ring in
+// shared memory (the next round's K and V rows are in flight while this one is computed).  A key / value row is
+// covered by hd/8 lanes with 16 bytes each, scores of the G = Hq / Hkv grouped heads are reduced with shuffles inside
+// those lanes (packed fp32 multiply-adds), the softmax is computed per round and the round's probabilities are fetched
+// back by shuffle for the P.V accumulation.  Partial (max, sum, acc) per warp are merged in shared memory and, when
+// the keys are split across CTAs, through an fp32 workspace: the last CTA of a (query row, kv head) to finish merges
+// the splits itself (arrival counter), so one kernel runs per call (attn_decode_merge_kernel remains for shapes beyond
+// the counter table).
 // The kernel is memory-bound by design: the roofline is the KV bytes over HBM bandwidth.
 #include <cuda_bf16.h>
 
 #include "common/host.h"
+#include "common/ptx.cuh"
 #include "common/reduce.cuh"
 
 namespace dptb {
@@ -38,6 +42,7 @@ struct DecodeArgs {
   const int* pos_ptr;        // when set: q_offset = *pos_ptr and Sk = q_offset + Sq (device-resident position, so a
                              // captured CUDA graph can be replayed as the sequence grows)
   int cap;                   // cache rows per sequence: no key at or beyond it is ever read
+  int fused_merge;           // the last split CTA of a (query row, kv head) merges the partials itself
 };
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
@@ -50,17 +55,44 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&f)[8]) {
   }
 }
 
+// Eight bf16 -> four packed fp32 pairs (operands of fma.rn.f32x2: half the multiply-add instructions of scalar code).
+__device__ __forceinline__ void unpack_bf16x8_f2(const uint4& u, f32x2 (&f)[4]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) f[i] = f2_pack(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+}
+
 // GP = grouped query heads padded to a power of two (heads >= G carry zero queries).  A key row is covered by
-// LPK = HD / 8 lanes with one 16-byte load each, so one load instruction of the warp fetches 32 / LPK keys; the loads
-// of eight iterations are issued before the first use (4 KB in flight per warp), which is what a latency-bound
-// streaming kernel needs.  Sub-group sg (LPK lanes) walks keys blk + LPK * sg + i, i < LPK: lane l ends up holding the
-// score of key blk + l, so the block softmax is two warp reductions and the probabilities are fetched back by shuffle.
+// LPK = HD / 8 lanes with 16 bytes each.  Every warp streams its keys in rounds of 16 through a private two-stage ring in
+// shared memory filled by cp.async (16 bytes per lane and instruction): the K and V rows of the next round are in
+// flight while this round is computed, so the loads of the resident warps overlap their arithmetic instead of
+// alternating with it, and no register holds data in flight.  Within a round sub-group sg (LPK lanes) owns keys
+// sg * KS + u, u < KS = LPK / 2; lane u of the sub-group ends up holding that key's scores, the round's softmax is two
+// warp reductions per head and the probabilities are fetched back by shuffle for P.V.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+constexpr int kDecRound = 16;    // keys per round of a warp
+
+// Arrival counters of the split CTAs of one (query row, kv head): the last CTA to arrive merges the partials, so no
+// second kernel runs.  Zero at load, reset by the merging CTA; launches that use them must not overlap on two streams.
+constexpr int kDecCounters = 1 << 16;
+__device__ unsigned int g_dec_counters[kDecCounters];
+constexpr int kDecMaxFusedSplits = 64;
+
 template <int HD, int GP>
 __global__ void __launch_bounds__(kDecWarps * 32, GP <= 4 ? 3 : 2)
 attn_decode_kernel(const DecodeArgs a) {
   constexpr int LPK = HD / 8;                // lanes per key
-  constexpr int U = 8;                       // key loads kept in flight per lane
-  static_assert(LPK % U == 0, "sub-group key count must be a multiple of the load batch");
+  constexpr int NSG = 32 / LPK;              // sub-groups per warp
+  constexpr int KS = kDecRound / NSG;        // keys per sub-group and round
+  constexpr int kStageChunks = kDecRound * LPK;            // 16-byte chunks of one K (or V) stage
+  constexpr int kWarpChunks = 4 * kStageChunks;            // two stages of K and V
+  extern __shared__ uint4 dec_ring[];
   const int split = blockIdx.x, g = blockIdx.y, bs = blockIdx.z;
   const int b = bs / a.Sq, sq = bs % a.Sq;
   const int G = a.Hq / a.Hkv;
@@ -75,111 +107,128 @@ attn_decode_kernel(const DecodeArgs a) {
   __shared__ float s_m[kDecWarps][GP], s_l[kDecWarps][GP];
   __shared__ float s_acc[kDecWarps][GP][HD];
 
-  float qv[GP][8];
+  f32x2 qv[GP][4];
   const __nv_bfloat16* qrow = a.q + (long long)bs * a.ldq + (long long)g * G * HD + sl * 8;
+  const f32x2 scale2 = f2_splat(a.scale);
 #pragma unroll
   for (int h = 0; h < GP; ++h) {
     if (h < G) {
-      unpack_bf16x8(*reinterpret_cast<const uint4*>(qrow + h * HD), qv[h]);
+      unpack_bf16x8_f2(*reinterpret_cast<const uint4*>(qrow + h * HD), qv[h]);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) qv[h][e] *= a.scale;
+      for (int e = 0; e < 4; ++e) qv[h][e] = f2_mul(qv[h][e], scale2);
     } else {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) qv[h][e] = 0.0f;
+      for (int e = 0; e < 4; ++e) qv[h][e] = f2_splat(0.0f);
     }
   }
-  float m[GP], l[GP], acc[GP][8];
+  float m[GP], l[GP];
+  f32x2 acc[GP][4];
 #pragma unroll
   for (int h = 0; h < GP; ++h) {
     m[h] = -INFINITY;
     l[h] = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[h][e] = 0.0f;
+    for (int e = 0; e < 4; ++e) acc[h][e] = f2_splat(0.0f);
   }
-  const __nv_bfloat16* kb = a.k + (long long)b * a.kv_batch_stride + (long long)g * HD + sl * 8;
-  const __nv_bfloat16* vb = a.v + (long long)b * a.kv_batch_stride + (long long)g * HD + sl * 8;
-
-  for (int blk = j0 + warp * 32; blk < j1; blk += kDecWarps * 32) {
-    const int key0 = blk + sg0;              // first key of this sub-group
-    // ---- scores: lane l keeps the score of key blk + l
+  const __nv_bfloat16* kb = a.k + (long long)b * a.kv_batch_stride + (long long)g * HD;
+  const __nv_bfloat16* vb = a.v + (long long)b * a.kv_batch_stride + (long long)g * HD;
+  uint4* ring = dec_ring + warp * kWarpChunks;   // [stage][K | V][16 rows][LPK chunks]
+  const int sg = lane / LPK;
+  const int rounds = (j1 - j0 + kDecRound - 1) / kDecRound;   // of this CTA; warp w takes rounds w, w + 4, ...
+  // Rows past the end of the range are fetched from the last valid row (finite data) and masked in the softmax.
+  auto issue = [&](int t, int stage) {
+    const int key0 = j0 + t * kDecRound;
+    uint4* dst = ring + stage * 2 * kStageChunks;
+#pragma unroll
+    for (int it = 0; it < kStageChunks / 32; ++it) {
+      const int c = it * 32 + lane;
+      const int key = min(key0 + c / LPK, j1 - 1);
+      const long long off = (long long)key * a.ldkv + (c % LPK) * 8;
+      cp_async_16(dst + c, kb + off);
+      cp_async_16(dst + kStageChunks + c, vb + off);
+    }
+    cp_async_commit();
+  };
+  if (warp < rounds) issue(warp, 0);
+  int it_local = 0;
+  for (int t = warp; t < rounds; t += kDecWarps, ++it_local) {
+    const int stage = it_local & 1;
+    if (t + kDecWarps < rounds) {
+      issue(t + kDecWarps, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncwarp();
+    const uint4* ks = ring + stage * 2 * kStageChunks;
+    const uint4* vs = ks + kStageChunks;
+    // ---- scores: lane u of a sub-group keeps the scores of key sg * KS + u of this round
     float sc[GP];
 #pragma unroll
     for (int h = 0; h < GP; ++h) sc[h] = -INFINITY;
-#pragma unroll 1
-    for (int i0 = 0; i0 < LPK; i0 += U) {
-      uint4 kr[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int key = key0 + i0 + u;
-        kr[u] = key < j1 ? *reinterpret_cast<const uint4*>(kb + (long long)key * a.ldkv) : make_uint4(0, 0, 0, 0);
-      }
+    for (int u = 0; u < KS; ++u) {
+      f32x2 kf[4];
+      unpack_bf16x8_f2(ks[(sg * KS + u) * LPK + sl], kf);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float kf[8];
-        unpack_bf16x8(kr[u], kf);
+      for (int h = 0; h < GP; ++h) {
+        f32x2 d2 = f2_mul(qv[h][0], kf[0]);
 #pragma unroll
-        for (int h = 0; h < GP; ++h) {
-          float d = 0.0f;
+        for (int e = 1; e < 4; ++e) d2 = f2_fma(qv[h][e], kf[e], d2);
+        float dlo, dhi;
+        f2_unpack(d2, dlo, dhi);
+        float d = dlo + dhi;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) d = fmaf(qv[h][e], kf[e], d);
-#pragma unroll
-          for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-          if (sl == i0 + u) sc[h] = d;
-        }
+        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (sl == u) sc[h] = d;
       }
     }
-    const bool live = blk + lane < j1;
-    // ---- block softmax statistics and rescale
+    const bool live = sl < KS && j0 + t * kDecRound + sg * KS + sl < j1;
+    // ---- round softmax statistics and rescale
     float p[GP];
 #pragma unroll
     for (int h = 0; h < GP; ++h) {
       const float s = live ? sc[h] : -INFINITY;
       const float nm = fmaxf(m[h], warp_max(s));
-      const float corr = __expf(m[h] - nm);             // 0 on the first block (m = -inf)
+      const float corr = __expf(m[h] - nm);             // 0 on the first round (m = -inf)
       p[h] = live ? __expf(s - nm) : 0.0f;
       l[h] = l[h] * corr + warp_sum(p[h]);
       m[h] = nm;
+      const f32x2 corr2 = f2_splat(corr);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[h][e] *= corr;
+      for (int e = 0; e < 4; ++e) acc[h][e] = f2_mul(acc[h][e], corr2);
     }
     // ---- P.V: every sub-group accumulates its own keys; the sub-groups are folded once at the end
-#pragma unroll 1
-    for (int i0 = 0; i0 < LPK; i0 += U) {
-      uint4 vr[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int key = key0 + i0 + u;
-        vr[u] = key < j1 ? *reinterpret_cast<const uint4*>(vb + (long long)key * a.ldkv) : make_uint4(0, 0, 0, 0);
-      }
+    for (int u = 0; u < KS; ++u) {
+      f32x2 vf[4];
+      unpack_bf16x8_f2(vs[(sg * KS + u) * LPK + sl], vf);
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float vf[8];
-        unpack_bf16x8(vr[u], vf);
+      for (int h = 0; h < GP; ++h) {
+        const f32x2 pj = f2_splat(__shfl_sync(0xffffffffu, p[h], sg0 + u));
 #pragma unroll
-        for (int h = 0; h < GP; ++h) {
-          const float pj = __shfl_sync(0xffffffffu, p[h], sg0 + i0 + u);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(pj, vf[e], acc[h][e]);
-        }
+        for (int e = 0; e < 4; ++e) acc[h][e] = f2_fma(pj, vf[e], acc[h][e]);
       }
     }
+    __syncwarp();   // every lane has read this stage before the load two rounds ahead overwrites it
   }
   // ---- fold the sub-groups of the warp, then the warps of the CTA (fixed order)
 #pragma unroll
-  for (int h = 0; h < GP; ++h)
+  for (int h = 0; h < GP; ++h) {
+    float af[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) f2_unpack(acc[h][e], af[2 * e], af[2 * e + 1]);
 #pragma unroll
     for (int e = 0; e < 8; ++e)
 #pragma unroll
-      for (int o = 16; o >= LPK; o >>= 1) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], o);
-#pragma unroll
-  for (int h = 0; h < GP; ++h) {
+      for (int o = 16; o >= LPK; o >>= 1) af[e] += __shfl_xor_sync(0xffffffffu, af[e], o);
     if (lane == 0) {
       s_m[warp][h] = m[h];
       s_l[warp][h] = l[h];
     }
     if (lane < LPK) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s_acc[warp][h][lane * 8 + e] = acc[h][e];
+      for (int e = 0; e < 8; ++e) s_acc[warp][h][lane * 8 + e] = af[e];
     }
   }
   __syncthreads();
@@ -205,6 +254,81 @@ attn_decode_kernel(const DecodeArgs a) {
         w[HD + 1] = ll;
       }
     }
+  }
+  if (a.splits == 1 || !a.fused_merge) return;
+  // ---- the last CTA of this (query row, kv head) to get here merges the splits (fixed order: deterministic)
+  __shared__ unsigned int s_last;
+  __shared__ float s_sm[kDecMaxFusedSplits][GP], s_sl[kDecMaxFusedSplits][GP];
+  __threadfence();   // this thread's partials are visible device-wide before the CTA is counted
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* ctr = &g_dec_counters[bs * a.Hkv + g];
+    const unsigned int prev = atomicAdd(ctr, 1u);
+    s_last = prev == (unsigned int)a.splits - 1u ? 1u : 0u;
+    if (s_last) *ctr = 0u;   // everyone has arrived: ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* base = a.ws + (((long long)bs * a.Hkv + g) * a.splits) * G * (HD + 2);
+  const long long sstride = (long long)G * (HD + 2);
+  for (int i = threadIdx.x; i < a.splits * G; i += blockDim.x) {
+    const int sp = i / G, h = i % G;
+    const float* w = base + sp * sstride + (long long)h * (HD + 2);
+    s_sm[sp][h] = __ldcg(w + HD);
+    s_sl[sp][h] = __ldcg(w + HD + 1);
+  }
+  __syncthreads();
+  // Every thread owns up to NO outputs (idx = thread + k * 128); the loads of all of them for two splits are issued
+  // together, so the merge is a few round trips to L2 instead of one per (output, split).
+  constexpr int NO = (GP * HD + kDecWarps * 32 - 1) / (kDecWarps * 32);
+  float mm[NO], ll[NO], oo[NO];
+  int hh[NO];
+  const float* wp[NO];
+#pragma unroll
+  for (int k = 0; k < NO; ++k) {
+    const int idx = threadIdx.x + k * (kDecWarps * 32);
+    const int h = idx / HD < G ? idx / HD : 0;       // padded heads repeat head 0 and are not stored
+    hh[k] = h;
+    wp[k] = base + (long long)h * (HD + 2) + idx % HD;
+    float m = -INFINITY;
+    for (int sp = 0; sp < a.splits; ++sp) m = fmaxf(m, s_sm[sp][h]);
+    mm[k] = m;
+    ll[k] = 0.0f;
+    oo[k] = 0.0f;
+  }
+  int sp = 0;
+  for (; sp + 2 <= a.splits; sp += 2) {
+    float v0[NO], v1[NO];
+#pragma unroll
+    for (int k = 0; k < NO; ++k) {
+      v0[k] = __ldcg(wp[k] + sp * sstride);
+      v1[k] = __ldcg(wp[k] + (sp + 1) * sstride);
+    }
+#pragma unroll
+    for (int k = 0; k < NO; ++k) {
+      const float m0 = s_sm[sp][hh[k]], m1 = s_sm[sp + 1][hh[k]];
+      const float c0 = m0 == -INFINITY ? 0.0f : __expf(m0 - mm[k]);
+      const float c1 = m1 == -INFINITY ? 0.0f : __expf(m1 - mm[k]);
+      ll[k] += s_sl[sp][hh[k]] * c0 + s_sl[sp + 1][hh[k]] * c1;
+      oo[k] += v0[k] * c0 + v1[k] * c1;
+    }
+  }
+  if (sp < a.splits) {
+#pragma unroll
+    for (int k = 0; k < NO; ++k) {
+      const float m0 = s_sm[sp][hh[k]];
+      const float c0 = m0 == -INFINITY ? 0.0f : __expf(m0 - mm[k]);
+      ll[k] += s_sl[sp][hh[k]] * c0;
+      oo[k] += __ldcg(wp[k] + sp * sstride) * c0;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NO; ++k) {
+    const int idx = threadIdx.x + k * (kDecWarps * 32);
+    if (idx / HD < G)
+      a.o[(long long)bs * a.ldo + (long long)(g * G + idx / HD) * HD + idx % HD] =
+          __float2bfloat16(ll[k] > 0.0f ? oo[k] / ll[k] : 0.0f);
   }
 }
 
@@ -304,13 +428,19 @@ extern "C" long long dptb_attn_decode_ws_floats(int B, int Sq, int Hq, int head_
 // Split count that fills the GPU once: three CTAs fit an SM (registers), and a grid beyond that runs a second, mostly
 // empty wave, so the count is rounded DOWN to what is resident at once; at least 128 keys (one 32-key block per warp)
 // per CTA.
-extern "C" int dptb_attn_decode_splits(int B, int Sq, int Hkv, int Sk) {
+static int decode_splits(int B, int Sq, int Hkv, int Sk, int head_dim) {
   const int base = B * Sq * Hkv;
-  int s = (3 * sm_count()) / base;
+  (void)head_dim;
+  const int per_sm = 3;   // CTAs resident per SM (registers): see the kernel's launch bounds
+  int s = (per_sm * sm_count()) / base;
   const int cap = (Sk + 127) / 128;
   if (s > cap) s = cap;
   if (s > 64) s = 64;
   return s < 1 ? 1 : s;
+}
+extern "C" int dptb_attn_decode_splits(int B, int Sq, int Hkv, int Sk) { return decode_splits(B, Sq, Hkv, Sk, 64); }
+extern "C" int dptb_attn_decode_splits_hd(int B, int Sq, int Hkv, int Sk, int head_dim) {
+  return decode_splits(B, Sq, Hkv, Sk, head_dim);
 }
 
 extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
@@ -337,8 +467,20 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
     return kErrTooLarge;
   dim3 grid(a.splits, a.Hkv, a.B * a.Sq);
   const int G = a.Hq / a.Hkv;
+  a.fused_merge = (a.splits > 1 && a.splits <= kDecMaxFusedSplits && (long long)a.B * a.Sq * a.Hkv <= kDecCounters) ? 1 : 0;
   const int gp = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8;
-#define DPTB_DEC(HDV, GPV) attn_decode_kernel<HDV, GPV><<<grid, kDecWarps * 32, 0, st>>>(a)
+  // ring: two stages of 16 K rows and 16 V rows per warp
+#define DPTB_DEC(HDV, GPV)                                                                                            \
+  do {                                                                                                                \
+    constexpr int kRing = kDecWarps * 4 * kDecRound * HDV * 2;                                                        \
+    static bool attr_set = false;                                                                                     \
+    if (!attr_set) {                                                                                                  \
+      DPTB_CUDA_OK(cudaFuncSetAttribute(attn_decode_kernel<HDV, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                        kRing));                                                                      \
+      attr_set = true;                                                                                                \
+    }                                                                                                                 \
+    attn_decode_kernel<HDV, GPV><<<grid, kDecWarps * 32, kRing, st>>>(a);                                             \
+  } while (0)
   if (h->head_dim == 128) {
     if (gp == 1) DPTB_DEC(128, 1); else if (gp == 2) DPTB_DEC(128, 2); else if (gp == 4) DPTB_DEC(128, 4); else DPTB_DEC(128, 8);
   } else {
@@ -346,7 +488,7 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
   }
 #undef DPTB_DEC
   DPTB_CUDA_OK(cudaGetLastError());
-  if (a.splits > 1) {
+  if (a.splits > 1 && !a.fused_merge) {
     dim3 mg(a.Hq, a.B * a.Sq);
     if (h->head_dim == 128) attn_decode_merge_kernel<128><<<mg, 128, 0, st>>>(a);
     else                    attn_decode_merge_kernel<64><<<mg, 128, 0, st>>>(a);

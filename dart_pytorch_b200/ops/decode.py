@@ -33,6 +33,8 @@ def _lib():
         lib.dptb_attn_decode_ws_floats.restype = c_ll
         lib.dptb_attn_decode_splits.argtypes = [c_int] * 4
         lib.dptb_attn_decode_splits.restype = c_int
+        lib.dptb_attn_decode_splits_hd.argtypes = [c_int] * 5
+        lib.dptb_attn_decode_splits_hd.restype = c_int
         lib.dptb_rope_kv_append.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll] + [c_int] * 7 + \
             [c_float, c_int, c_void_p, c_void_p]
         lib.dptb_rope_kv_append.restype = c_int
@@ -82,7 +84,7 @@ def attn_decode(q2: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     if out is None:
         out = torch.empty(B * Sq, Hq * hd, dtype=torch.bfloat16, device=q2.device)
     if splits <= 0:
-        splits = int(lib.dptb_attn_decode_splits(B, Sq, Hkv, Sk))
+        splits = int(lib.dptb_attn_decode_splits_hd(B, Sq, Hkv, Sk, hd))
     need = int(lib.dptb_attn_decode_ws_floats(B, Sq, Hq, hd, splits))
     if need and (workspace is None or workspace.numel() < need):
         workspace = torch.empty(need, dtype=torch.float32, device=q2.device)
@@ -101,7 +103,7 @@ def attn_decode(q2: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 def decode_workspace_floats(B: int, Sq: int, Hq: int, Hkv: int, hd: int, max_sk: int) -> int:
     """Workspace size that covers every context length up to ``max_sk`` (for preallocation before graph capture)."""
     lib = _lib()
-    splits = int(lib.dptb_attn_decode_splits(B, Sq, Hkv, max_sk))
+    splits = int(lib.dptb_attn_decode_splits_hd(B, Sq, Hkv, max_sk, hd))
     return int(lib.dptb_attn_decode_ws_floats(B, Sq, Hq, hd, max(splits, 1)))
 
 
