@@ -290,7 +290,7 @@ class ExpertParallelMoE(Module):
         self._comm: Optional[EpComm] = None
         self._tokens = tokens_per_rank
         self.aux_loss = None
-        self.last_dropped = None
+        self._dropped = None
 
     def own_parameters(self):
         return [self.gate] + self.w_gate_up + self.w_down
@@ -320,6 +320,11 @@ class ExpertParallelMoE(Module):
             self._comm = EpComm(self.E, C, self.dim, self.group)
         return self._comm
 
+    @property
+    def last_dropped(self):
+        """Routed (token, expert) pairs of the last forward that did not fit their expert's quota (synchronises)."""
+        return None if self._dropped is None else int(self._dropped.item())
+
     def forward(self, x):
         shape = x.shape
         x2 = x.reshape(-1, self.dim)
@@ -344,9 +349,12 @@ class ExpertParallelMoE(Module):
         y = EpCombineFn.apply(rows_out, w, comm, idx, slot, count, counts_here)
         # load-balance auxiliary loss: E * sum_e f_e * P_e, f_e from the routed (not yet capacity-clipped) pairs
         with torch.no_grad():
-            counts = torch.bincount(idx.reshape(-1).long(), minlength=self.E).float()
+            flat = idx.reshape(-1).long()
+            # (scatter_add, not bincount: bincount reads its output size back to the host, a synchronisation per layer)
+            counts = torch.zeros(self.E, dtype=torch.float32, device=flat.device).scatter_add_(
+                0, flat, torch.ones(flat.numel(), dtype=torch.float32, device=flat.device))
             self._expert_load += counts
             f = counts / float(T * self.k)
-            self.last_dropped = int((slot < 0).sum().item()) if not torch.cuda.is_current_stream_capturing() else None
+            self._dropped = (slot < 0).sum()      # read lazily (``last_dropped``): no host synchronisation per layer
         self.aux_loss = self.aux_loss_coef * self.E * (f * probs.mean(0)).sum()
         return y.reshape(shape)
