@@ -93,6 +93,8 @@ attn_decode_kernel(const DecodeArgs a) {
   constexpr int kStageChunks = kDecRound * LPK;            // 16-byte chunks of one K (or V) stage
   constexpr int kWarpChunks = 4 * kStageChunks;            // two stages of K and V
   extern __shared__ uint4 dec_ring[];
+  pdl_wait();                // (programmatic dependent launch: no-ops in an ordinary launch)
+  pdl_launch_dependents();
   const int split = blockIdx.x, g = blockIdx.y, bs = blockIdx.z;
   const int b = bs / a.Sq, sq = bs % a.Sq;
   const int G = a.Hq / a.Hkv;
@@ -362,6 +364,8 @@ __global__ void __launch_bounds__(128)
 rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, __nv_bfloat16* __restrict__ kc,
                       __nv_bfloat16* __restrict__ vc, long long ldkv, long long kv_batch_stride, int B, int S, int Hq,
                       int Hkv, int pos0, int rotary_dim, float base, int cap, const int* __restrict__ pos_ptr) {
+  pdl_wait();                // (programmatic dependent launch: no-ops in an ordinary launch)
+  pdl_launch_dependents();
   const int row = blockIdx.x;                // b * S + s
   const int b = row / S, s = row % S;
   const int pos = (pos_ptr ? *pos_ptr : pos0) + s;
@@ -479,7 +483,7 @@ extern "C" int dptb_attn_decode(const DptbDecodeArgs* h, void* stream) {
                                         kRing));                                                                      \
       attr_set = true;                                                                                                \
     }                                                                                                                 \
-    attn_decode_kernel<HDV, GPV><<<grid, kDecWarps * 32, kRing, st>>>(a);                                             \
+    DPTB_CUDA_OK(launch_k(attn_decode_kernel<HDV, GPV>, grid, dim3(kDecWarps * 32), kRing, st, a));                   \
   } while (0)
   if (h->head_dim == 128) {
     if (gp == 1) DPTB_DEC(128, 1); else if (gp == 2) DPTB_DEC(128, 2); else if (gp == 4) DPTB_DEC(128, 4); else DPTB_DEC(128, 8);
@@ -508,9 +512,9 @@ extern "C" int dptb_rope_kv_append(void* qkv, long long ld, void* kc, void* vc, 
   auto* k = static_cast<__nv_bfloat16*>(kc);
   auto* v = static_cast<__nv_bfloat16*>(vc);
   if (head_dim == 128)
-    rope_kv_append_kernel<128><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap, pos_ptr);
+    DPTB_CUDA_OK(launch_k(rope_kv_append_kernel<128>, dim3(B * S), dim3(128), 0, st, q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap, pos_ptr));
   else if (head_dim == 64)
-    rope_kv_append_kernel<64><<<B * S, 128, 0, st>>>(q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap, pos_ptr);
+    DPTB_CUDA_OK(launch_k(rope_kv_append_kernel<64>, dim3(B * S), dim3(128), 0, st, q, ld, k, v, ldkv, kv_batch_stride, B, S, Hq, Hkv, pos0, rotary_dim, base, cap, pos_ptr));
   else
     return kErrUnsupported;
   return counted(1, (int)cudaGetLastError());

@@ -107,4 +107,42 @@ inline int sm_count() {
   return cached[dev];
 }
 
+// Whether the kernels that support it are launched as programmatic dependents of their predecessor on the stream
+// (see pdl_wait below).  Off by default; the tensor-parallel decode engine turns it on around its step.
+inline int& pdl_flag() {
+  static int on = 0;
+  return on;
+}
+
+#ifdef __CUDACC__
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor on the stream is still running: everything it does before pdl_wait() (barrier set-up, TMEM
+// allocation, loads of data the predecessor does not write) overlaps the predecessor's tail; pdl_wait() returns once
+// the predecessor has completed and its writes are visible.  pdl_launch_dependents() in the predecessor lets such a
+// dependent start early.  Both are no-ops in launches without the attribute / without such a dependent.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Launches `kern`, as a programmatic dependent of the previous kernel on the stream when pdl_flag() is set.  Such a
+// kernel calls pdl_wait() before its first global access and pdl_launch_dependents() after it, never before: the kernel
+// after it must not start while the kernel two places back is still running.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  if (!pdl_flag()) {
+    kern<<<grid, block, smem, st>>>(args...);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 }  // namespace dptb

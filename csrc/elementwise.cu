@@ -365,6 +365,8 @@ template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
 swiglu_fwd_vec8_kernel(const T* __restrict__ g, long long ldg, const T* __restrict__ u, long long ldu,
                        T* __restrict__ out, long long ldo, long long rows, int cols) {
+  pdl_wait();                // (programmatic dependent launch: no-ops in an ordinary launch)
+  pdl_launch_dependents();
   const int cv = cols >> 3;
   const long long n = rows * cv;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -729,7 +731,7 @@ extern "C" int dptb_swiglu_fwd(const void* g, long long ldg, const void* u, long
   if (vec8_ok(cols, {ldg, ldu, ldo}, {g, u, out}, dtype ? 2 : 4)) {
     const long long nv = rows * (cols >> 3);
     DPTB_BY_DTYPE(dtype,
-                  (swiglu_fwd_vec8_kernel<__nv_bfloat16><<<ew_grid(nv), kEwThreads, 0, st>>>((const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)out, ldo, rows, cols)),
+                  (launch_k(swiglu_fwd_vec8_kernel<__nv_bfloat16>, dim3(ew_grid(nv)), dim3(kEwThreads), 0, st, (const __nv_bfloat16*)g, ldg, (const __nv_bfloat16*)u, ldu, (__nv_bfloat16*)out, ldo, rows, cols)),
                   (swiglu_fwd_vec8_kernel<float><<<ew_grid(nv), kEwThreads, 0, st>>>((const float*)g, ldg, (const float*)u, ldu, (float*)out, ldo, rows, cols)));
     return counted(1, (int)cudaGetLastError());
   }

@@ -151,6 +151,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint32_t os_epoch = p.os.world > 0 ? *reinterpret_cast<volatile uint32_t*>(p.os.epoch) + 1u : 0u;
 
   SK_STAMP(0, blockIdx.x == 0 && threadIdx.x == 0);
+  pdl_launch_dependents();   // the small kernel after this one waits for this grid's completion at its own top
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *epi_ctr = 0;
@@ -180,8 +181,19 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = kb0; kb < kb1; ++kb, ++issued) {
+      // The weights do not depend on the kernel before this one: the first ring-full of weight tiles is requested at
+      // once, then (programmatic dependent launch) the predecessor's completion is awaited, then the activation
+      // tiles of those stages follow.  Every stage's barrier expects both tiles.
+      const int pre = max(0, min(kb1 - kb0, kSkStages));
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&full_bar[i], L::kStage);
+        tma_load_2d(smem + i * L::kStage, &tmW, &full_bar[i], (kb0 + i) * kSkBK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * L::kStage + L::kWBytes, &tmX, &full_bar[i], (kb0 + i) * kSkBK, 0);
+      int issued = pre;
+      for (int kb = kb0 + pre; kb < kb1; ++kb, ++issued) {
         const int s = issued % kSkStages;
         const uint32_t ph = (issued / kSkStages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, kWaitEmptyTimeout)) break;
@@ -231,6 +243,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (one TMEM lane quarter each)
+    pdl_wait();   // nothing below may touch global memory before the predecessor has completed (an empty K range
+                  // reaches the stores without passing through the producer's wait)
     const int q = warp & 3;
     const int n_local = q * 32 + lane;
     const int et = threadIdx.x - 64;           // 0..127 among the epilogue threads
@@ -528,13 +542,17 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
     DPTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  kern<<<units, kSkThreads, L::kTotal, stream>>>(tmW, tmX, p);
-  return counted(1, (int)cudaGetLastError());
+  return counted(1, (int)launch_k(kern, dim3(units), dim3(kSkThreads), L::kTotal, stream, tmW, tmX, p));
 }
 
 }  // namespace dptb
 
 using namespace dptb;
+
+// Turns programmatic dependent launch on or off for the kernels of the decode step (this kernel, RMSNorm, rotary +
+// cache append, decode attention, SwiGLU).  The caller keeps it on only around a chain in which the kernel before an
+// all-reduce GEMM is never another all-reduce GEMM (this kernel reads its protocol counters before its wait).
+extern "C" void dptb_gemm_skinny_set_pdl(int on) { dptb::pdl_flag() = on ? 1 : 0; }
 
 // Peer-memory description of the one-shot all-reduce (see SkinnyOneShot); every rank's slot buffer holds
 // 2 * kMaxRanks * max_tiles * 64 * 128 eight-byte words, zero-initialised.

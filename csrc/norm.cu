@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(kNormThreads, 3)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
                 float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows, int D, float eps) {
   __shared__ float scratch[33];
+  pdl_wait();                // (programmatic dependent launch: no-ops in an ordinary launch)
+  pdl_launch_dependents();
   constexpr int RPB = kNormThreads / G;
   const int g = threadIdx.x / G, t = threadIdx.x % G;
   const int nvec = D / 8;
@@ -321,12 +323,12 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
   if (al && D % 8 == 0 && nvec <= 32 * kNormMaxVec) {
     long long blocks = (rows + 7) / 8;
     if (blocks > nsm * 8) blocks = nsm * 8;
-    DPTB_NORM_DISPATCH_V((nvec + 31) / 32, (norm_fwd_kernel<T, 32, V, RMS><<<(int)blocks, kNormThreads, 0, st>>>(
-        (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps)));
+    DPTB_NORM_DISPATCH_V((nvec + 31) / 32, (launch_k(norm_fwd_kernel<T, 32, V, RMS>, dim3((int)blocks), dim3(kNormThreads), 0, st,
+                 (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps)));
   } else if (al && D % 8 == 0 && nvec <= 256 * kNormMaxVec) {
     long long blocks = rows < nsm * 8 ? rows : nsm * 8;
-    DPTB_NORM_DISPATCH_V((nvec + 255) / 256, (norm_fwd_kernel<T, 256, V, RMS><<<(int)blocks, kNormThreads, 0, st>>>(
-        (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps)));
+    DPTB_NORM_DISPATCH_V((nvec + 255) / 256, (launch_k(norm_fwd_kernel<T, 256, V, RMS>, dim3((int)blocks), dim3(kNormThreads), 0, st,
+                 (const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps)));
   } else {
     long long blocks = rows < nsm * 8 ? rows : nsm * 8;
     norm_fwd_generic_kernel<T, RMS><<<(int)blocks, kNormThreads, 0, st>>>((const T*)x, (const T*)gamma, (const T*)beta, (T*)y, mean, rstd, rows, D, eps);

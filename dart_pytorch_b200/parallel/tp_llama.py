@@ -23,6 +23,7 @@ never returns to the host and is captured in a CUDA graph (the position lives in
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -287,10 +288,18 @@ class TPLlamaEngine:
         return self.tokens[:B].clone()
 
     def _decode_body(self, B: int) -> None:
-        x = self.comm.buffer(0, B)
-        x.copy_(K.embedding_fwd(self.embed, self.tokens[:B]))
-        xo = self._blocks(x, B, 1, 0, device_pos=True)
-        self._head(xo, B, advance=1)
+        # The weight-streaming GEMMs of the step are launched as programmatic dependents of the small kernel before
+        # them (norm, attention, SwiGLU): their set-up and first ring-full of weight tiles overlap that kernel.
+        pdl = os.environ.get("DPTB200_TP_PDL", "1") != "0"
+        lib = N.load()
+        lib.dptb_gemm_skinny_set_pdl(1 if pdl else 0)
+        try:
+            x = self.comm.buffer(0, B)
+            x.copy_(K.embedding_fwd(self.embed, self.tokens[:B]))
+            xo = self._blocks(x, B, 1, 0, device_pos=True)
+            self._head(xo, B, advance=1)
+        finally:
+            lib.dptb_gemm_skinny_set_pdl(0)
 
     @torch.no_grad()
     def decode_step(self, B: int, use_graph: bool = True) -> torch.Tensor:

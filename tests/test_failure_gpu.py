@@ -24,7 +24,7 @@ def test_flag_wait_times_out_into_status_word():
     N.raise_on_device_error()
     t0 = time.time()
     N.check(lib.dptb_dp_finalize(pad.data_ptr(), epochs.data_ptr(), nb, world, ctypes.c_float(1.0), ctrl.data_ptr(),
-                                 N.stream_ptr()), "dp_finalize")
+                                 0, N.stream_ptr()), "dp_finalize")          # wait limit 0: the default (one second)
     torch.cuda.synchronize()
     took = time.time() - t0
     assert 0.5 < took < 10.0                      # the wait is bounded (about one second), not endless
