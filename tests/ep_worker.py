@@ -16,7 +16,12 @@ from dart_pytorch_b200.parallel.ep import ExpertParallelMoE, capacity  # noqa: E
 def reference(x, gate, wgu, wd, k, C, coef):
     """fp32: x [T, D]; gate [E, D]; wgu[e] [2H, D]; wd[e] [D, H]."""
     T, E = x.shape[0], gate.shape[0]
-    probs = torch.softmax(x @ gate.t(), -1)
+    # The layer's router GEMM writes bf16 logits; the choice of experts is made on those.  The reference rounds its fp32
+    # logits the same way (straight-through for the gradient), so that a near-tie between two experts cannot route a
+    # token differently on the two sides (with 16 experts such near-ties do occur among a few thousand tokens).
+    logits = x @ gate.t()
+    logits = logits + (logits.bfloat16().float() - logits).detach()
+    probs = torch.softmax(logits, -1)
     w, idx = torch.topk(probs, k, dim=-1)                 # ties: lowest index first (as the kernel)
     y = torch.zeros_like(x)
     seen = [0] * E
@@ -49,7 +54,7 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    D, H, E, k, T = 64, 128, 2 * world, 2, 96
+    D, H, E, k, T = 64, 128, int(os.environ.get("DPTB200_EP_TEST_EXPERTS", 2 * world)), 2, 96
     cf = float(sys.argv[1]) if len(sys.argv) > 1 else 1.25
     moe = ExpertParallelMoE(D, H, E, top_k=k, capacity_factor=cf, aux_loss_coef=0.01, device="cuda", seed=5,
                             dtype=torch.bfloat16)
@@ -111,4 +116,8 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except Exception as e:  # one line the launcher's summary cannot bury
+        print(f"EP_WORKER_FAIL rank {os.environ.get('RANK')}: {e!r}", flush=True)
+        raise

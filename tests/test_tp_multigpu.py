@@ -15,7 +15,11 @@ def _run(script: str, mode: str, nproc: int = 2, port: int = 29543, ok: str = "o
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, script), mode]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
-    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    if proc.returncode != 0:
+        # the launcher's summary floods the tail: show the workers' own error lines first
+        lines = (proc.stdout + "\n" + proc.stderr).splitlines()
+        errs = [ln for ln in lines if "Error" in ln or "WORKER_FAIL" in ln or "assert" in ln.lower()]
+        raise AssertionError("\n".join(errs[:40]) + "\n...\n" + proc.stdout[-1500:] + proc.stderr[-1500:])
     assert ok in proc.stdout
 
 
