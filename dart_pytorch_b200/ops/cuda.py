@@ -8,6 +8,7 @@ accumulates in its epilogue and autograd receives ``None`` for that input.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -66,6 +67,54 @@ def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, needs: bo
     return dw
 
 
+# Bias gradients on a side stream.  The column sums of an upstream gradient are memory-bound and nothing in the backward
+# pass waits for them, while the weight- and data-gradient GEMMs beside them are compute-bound: the sums are launched on
+# a side stream forked from the current one and joined after those GEMMs, so they run on the SMs that a GEMM's last wave
+# leaves idle (-1 to -3 % on the GPT-2 step over three A / B runs).  Only gradients accumulated straight into an optimizer arena take this path (no
+# tensor changes streams).  Moving the weight-gradient GEMMs there as well was measured and gained less (-0.7 %): two
+# persistent GEMMs then compete for the same SMs.  DPTB200_GRAD_SIDE_STREAM=0 turns it off.
+_GRAD_SIDE = os.environ.get("DPTB200_GRAD_SIDE_STREAM", "1") != "0"
+_side_streams = {}
+
+
+class _ParamGradFork:
+    """``with`` block whose body runs on the side stream, after everything queued on the current stream so far;
+    ``join()`` makes the current stream wait for it."""
+
+    def __init__(self, device):
+        self.cur = torch.cuda.current_stream(device)
+        key = device.index
+        side = _side_streams.get(key)
+        if side is None:
+            side = _side_streams[key] = torch.cuda.Stream(device=device)
+        self.side = side
+        self.used = False
+
+    def __enter__(self):
+        self.side.wait_stream(self.cur)
+        self.used = True
+        self._ctx = torch.cuda.stream(self.side)
+        self._ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        return self._ctx.__exit__(*exc)
+
+    def join(self):
+        if self.used:
+            self.cur.wait_stream(self.side)
+
+
+def _bias_grad_fork(dy2, b, needs: bool, fork: Optional[_ParamGradFork]):
+    """The bias gradient, on the fork's side stream when it accumulates straight into an arena (returns None then, as
+    ``_bias_grad`` does for such a parameter)."""
+    if fork is None or b is None or not needs or _direct_grad(b) is None:
+        return _bias_grad(dy2, b, needs)
+    with fork:
+        _bias_grad(dy2, b, needs)
+    return None
+
+
 def _bias_grad(dy2: torch.Tensor, b: Optional[torch.Tensor], needs: bool):
     if b is None or not needs:
         return None
@@ -111,13 +160,16 @@ class LinearFn(torch.autograd.Function):
         w, b, act = ctx.w, ctx.b, ctx.act
         dy2 = _as2d(dy)
         dpre = K.unary_bwd(pre, dy2, act) if act else dy2
+        fork = _ParamGradFork(dy2.device) if (_GRAD_SIDE and dy2.is_cuda) else None
+        db = _bias_grad_fork(dpre, b, ctx.needs_input_grad[2], fork)
         dx = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x2)
             K.gemm(dpre, w, dx)
             dx = dx.view(ctx.xshape)
         dw = _weight_grad(dpre, x2, w, ctx.needs_input_grad[1])
-        db = _bias_grad(dpre, b, ctx.needs_input_grad[2])
+        if fork is not None:
+            fork.join()
         dres = dy if ctx.has_res and ctx.needs_input_grad[4] else None
         return dx, dw, db, None, dres
 
@@ -155,16 +207,21 @@ class MLPFn(torch.autograd.Function):
         w1, b1, w2, b2 = ctx.params
         dy2 = _as2d(dy)
         dpre = torch.empty_like(pre)
+        fork = _ParamGradFork(dy2.device) if (_GRAD_SIDE and dy2.is_cuda) else None
+        db2 = _bias_grad_fork(dy2, b2, ctx.needs_input_grad[4], fork)       # beside the next two GEMMs
         K.gemm(dy2, w2, dpre, aux_in=pre, act_bwd="mul" if ctx.act == "gelu_tanh" else ctx.act)
         dw2 = _weight_grad(dy2, a, w2, ctx.needs_input_grad[3])
-        db2 = _bias_grad(dy2, b2, ctx.needs_input_grad[4])
+        if fork is not None:
+            fork.join()
+        db1 = _bias_grad_fork(dpre, b1, ctx.needs_input_grad[2], fork)      # dpre is complete: beside the last two
         dw1 = _weight_grad(dpre, x2, w1, ctx.needs_input_grad[1])
-        db1 = _bias_grad(dpre, b1, ctx.needs_input_grad[2])
         dx = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x2)
             K.gemm(dpre, w1, dx)
             dx = dx.view(ctx.xshape)
+        if fork is not None:
+            fork.join()
         dres = dy if ctx.has_res and ctx.needs_input_grad[6] else None
         return dx, dw1, db1, dw2, db2, None, dres
 

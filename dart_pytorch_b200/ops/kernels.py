@@ -35,9 +35,11 @@ SPLITK_COUNTERS = 4096
 
 
 def splitk_workspace(device: torch.device):
-    """Per-device scratch of the split-K GEMM path: an fp32 partial-tile buffer and zeroed per-tile counters.  Launches
-    on one stream reuse it in order; the counters return to zero at the end of every launch."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    """Scratch of the split-K GEMM path, one per (device, stream): an fp32 partial-tile buffer and zeroed per-tile
+    counters.  Launches on one stream reuse it in order (the counters return to zero at the end of every launch);
+    GEMMs launched on another stream (weight gradients beside the data-gradient chain) get their own."""
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
     ws = _SPLITK_WS.get(key)
     if ws is None:
         ws = (torch.empty(SPLITK_WS_BYTES, dtype=torch.uint8, device=device),
