@@ -52,14 +52,28 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.path = index, None, f"/tmp/dptb_clocks_{os.getpid()}.csv"
+        self.first_line = 0
 
     def start(self):
+        """Starts sampling if it is not running yet (nvidia-smi needs a few hundred ms before its first line: a caller
+        with a short timed region starts it during warm-up and calls ``mark()`` where the region begins)."""
+        if self.proc is not None:
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+
+    def mark(self):
+        """The timed region begins here: only lines written from now on are summarised."""
+        self.start()
+        try:
+            with open(self.path) as f:
+                self.first_line = sum(1 for _ in f)
+        except OSError:
+            self.first_line = 0
 
     def stop(self):
         if self.proc is None:
@@ -72,7 +86,10 @@ class ClockSampler:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         try:
-            for line in open(self.path):
+            lines = open(self.path).read().splitlines()
+            # the timed window; if it was too short to catch a line, the last samples before it (same load: warm-up)
+            window = lines[self.first_line:] or lines[max(0, self.first_line - 3):]
+            for line in window:
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) < 7:
                     continue
@@ -159,18 +176,20 @@ def run_ours(args):
     dx, dy = hx.cuda(), hy.cuda()
     tokens_per_step = args.batch * SEQ * world
 
-    # Warm-up (eager steps, then graph capture).
+    # Warm-up (eager steps, then graph capture); the clock sampler is already running, the timed region is marked below.
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     for i in range(max(args.warmup, 3)):
         loss = trainer.step(dx[i % n_batches], dy[i % n_batches])
     barrier(world)
     first_loss = float(loss)
 
     # ---- device-timed region: inputs already on the device -------------------------------------------
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches_before = lib.dptb_launch_count()
     barrier(world)
+    if rank == 0:
+        sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):

@@ -121,11 +121,13 @@ def measure(model_cfg, seq, world, local, batch, steps, warmup, hx, hy, dx, dy, 
     tr = TorchTrainer(model_cfg, world, local, batch, seq, use_graph=use_graph)
     n_batches = dx.shape[0]
     tr.warm_and_capture(dx[0], dy[0])
+    if sampler is not None:
+        sampler.start()          # running through the warm-up; the timed region is marked below
     for i in range(max(warmup, 3)):
         loss = tr.step(dx[i % n_batches], dy[i % n_batches])
     barrier(world)
     if sampler is not None:
-        sampler.start()
+        sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
