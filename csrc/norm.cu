@@ -343,7 +343,7 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
 template <typename T, bool RMS>
 static int norm_bwd_launch(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
                            const void* dres, void* dx, void* dgamma, void* dbeta, float* partial, int partial_rows,
-                           int accumulate, long long rows, int D, cudaStream_t st) {
+                           int accumulate, long long rows, int D, cudaStream_t st, int stage1_only, int* nparts_out) {
   if (rows <= 0) return 0;
   const bool al = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
                     reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(dres)) & 15) == 0;
@@ -368,6 +368,8 @@ static int norm_bwd_launch(const void* x, const void* dy, const void* gamma, con
     norm_bwd_generic_kernel<T, RMS><<<blocks, kNormThreads, 0, st>>>((const T*)x, (const T*)dy, (const T*)gamma, mean, rstd, (const T*)dres, (T*)dx, partial, rows, D);
   }
   DPTB_CUDA_OK(cudaGetLastError());
+  if (nparts_out) *nparts_out = blocks;
+  if (stage1_only) return counted(1, 0);   // the caller runs the parameter-gradient reduction itself (another stream)
   norm_param_grad_reduce_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(partial, blocks, D, (T*)dgamma, RMS ? (T*)nullptr : (T*)dbeta, accumulate);
   return counted(2, (int)cudaGetLastError());
 }
@@ -390,18 +392,32 @@ extern "C" int dptb_rmsnorm_fwd(const void* x, const void* gamma, void* y, float
                : norm_fwd_launch<float, true>(x, gamma, nullptr, y, nullptr, rstd, rows, D, eps, st);
 }
 // partial: fp32 scratch of partial_rows * 2 * D floats.  dres (optional) is added to dx (residual-stream gradient).
+// stage1_only: stop after the kernel that writes dx and the per-CTA partials; *nparts_out receives the number of
+// partial rows it wrote, and dptb_norm_param_grad_reduce finishes dgamma / dbeta later (on any stream that is ordered
+// after this launch).
 extern "C" int dptb_layernorm_bwd(const void* x, const void* dy, const void* gamma, const float* mean,
                                   const float* rstd, const void* dres, void* dx, void* dgamma, void* dbeta,
                                   float* partial, int partial_rows, int accumulate, long long rows, int D, int dtype,
-                                  void* stream) {
+                                  void* stream, int stage1_only, int* nparts_out) {
   auto st = static_cast<cudaStream_t>(stream);
-  return dtype ? norm_bwd_launch<__nv_bfloat16, false>(x, dy, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, partial_rows, accumulate, rows, D, st)
-               : norm_bwd_launch<float, false>(x, dy, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, partial_rows, accumulate, rows, D, st);
+  return dtype ? norm_bwd_launch<__nv_bfloat16, false>(x, dy, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, partial_rows, accumulate, rows, D, st, stage1_only, nparts_out)
+               : norm_bwd_launch<float, false>(x, dy, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, partial_rows, accumulate, rows, D, st, stage1_only, nparts_out);
 }
 extern "C" int dptb_rmsnorm_bwd(const void* x, const void* dy, const void* gamma, const float* rstd, const void* dres,
                                 void* dx, void* dgamma, float* partial, int partial_rows, int accumulate,
-                                long long rows, int D, int dtype, void* stream) {
+                                long long rows, int D, int dtype, void* stream, int stage1_only, int* nparts_out) {
   auto st = static_cast<cudaStream_t>(stream);
-  return dtype ? norm_bwd_launch<__nv_bfloat16, true>(x, dy, gamma, nullptr, rstd, dres, dx, dgamma, nullptr, partial, partial_rows, accumulate, rows, D, st)
-               : norm_bwd_launch<float, true>(x, dy, gamma, nullptr, rstd, dres, dx, dgamma, nullptr, partial, partial_rows, accumulate, rows, D, st);
+  return dtype ? norm_bwd_launch<__nv_bfloat16, true>(x, dy, gamma, nullptr, rstd, dres, dx, dgamma, nullptr, partial, partial_rows, accumulate, rows, D, st, stage1_only, nparts_out)
+               : norm_bwd_launch<float, true>(x, dy, gamma, nullptr, rstd, dres, dx, dgamma, nullptr, partial, partial_rows, accumulate, rows, D, st, stage1_only, nparts_out);
+}
+// Second stage on its own: dgamma (and dbeta, unless null) (+)= column sums of the nparts partial rows.
+extern "C" int dptb_norm_param_grad_reduce(const float* partial, int nparts, int D, void* dgamma, void* dbeta,
+                                           int accumulate, int dtype, void* stream) {
+  auto st = static_cast<cudaStream_t>(stream);
+  if (nparts <= 0 || D <= 0) return 0;
+  if (dtype)
+    norm_param_grad_reduce_kernel<__nv_bfloat16><<<(D + 31) / 32, 256, 0, st>>>(partial, nparts, D, (__nv_bfloat16*)dgamma, (__nv_bfloat16*)dbeta, accumulate);
+  else
+    norm_param_grad_reduce_kernel<float><<<(D + 31) / 32, 256, 0, st>>>(partial, nparts, D, (float*)dgamma, (float*)dbeta, accumulate);
+  return counted(1, (int)cudaGetLastError());
 }

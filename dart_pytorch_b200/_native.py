@@ -150,8 +150,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("dptb_status_clear")
     sig("dptb_layernorm_fwd", P, P, P, P, P, P, L, I, F, I, P)
     sig("dptb_rmsnorm_fwd", P, P, P, P, L, I, F, I, P)
-    sig("dptb_layernorm_bwd", P, P, P, P, P, P, P, P, P, P, I, I, L, I, I, P)
-    sig("dptb_rmsnorm_bwd", P, P, P, P, P, P, P, P, I, I, L, I, I, P)
+    sig("dptb_layernorm_bwd", P, P, P, P, P, P, P, P, P, P, I, I, L, I, I, P, I, P)
+    sig("dptb_norm_param_grad_reduce", P, I, I, P, P, I, I, P)
+    sig("dptb_rmsnorm_bwd", P, P, P, P, P, P, P, P, I, I, L, I, I, P, I, P)
     sig("dptb_ce_fwd", P, L, P, P, P, L, I, I, P)
     sig("dptb_ce_bwd", P, L, P, P, P, I, F, P, L, L, I, I, I, P)
     sig("dptb_softmax_fwd", P, P, L, I, I, P)

@@ -67,13 +67,17 @@ def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor, needs: bo
     return dw
 
 
-# Bias gradients on a side stream.  The column sums of an upstream gradient are memory-bound and nothing in the backward
-# pass waits for them, while the weight- and data-gradient GEMMs beside them are compute-bound: the sums are launched on
-# a side stream forked from the current one and joined after those GEMMs, so they run on the SMs that a GEMM's last wave
-# leaves idle (-1 to -3 % on the GPT-2 step over three A / B runs).  Only gradients accumulated straight into an optimizer arena take this path (no
-# tensor changes streams).  Moving the weight-gradient GEMMs there as well was measured and gained less (-0.7 %): two
-# persistent GEMMs then compete for the same SMs.  DPTB200_GRAD_SIDE_STREAM=0 turns it off.
+# Parameter-gradient tails on a side stream.  The column sums of an upstream gradient (bias gradients) and the reduction
+# of the norm layers' per-CTA partials into dgamma / dbeta are memory-bound and nothing in the backward pass waits for
+# them, while the GEMMs beside them are compute-bound.  They are launched on a side stream forked from the current one:
+# the bias sums are joined after the GEMMs of their own autograd node, the norm reductions at the next such join or at
+# the end of the backward pass (engine callback), so both run on the SMs that a GEMM's last wave leaves idle.  Measured on
+# the GPT-2 step, same box: 20.83 -> 20.79 ms with the bias sums alone (within noise), -> 20.53 ms with the norm
+# reductions as well; on 2 GPUs 21.55 -> 21.0 ms.  Only gradients accumulated straight into an optimizer arena take this
+# path (no tensor changes streams).  Moving the weight-gradient GEMMs there too gained less: two persistent GEMMs then
+# compete for the same SMs.  DPTB200_GRAD_SIDE_STREAM=0 turns all of it off, DPTB200_NORM_DEFER=0 the norm part.
 _GRAD_SIDE = os.environ.get("DPTB200_GRAD_SIDE_STREAM", "1") != "0"
+_NORM_DEFER = os.environ.get("DPTB200_NORM_DEFER", "1") != "0"      # the norm parameter-gradient reduction as well
 _side_streams = {}
 
 
@@ -103,6 +107,39 @@ class _ParamGradFork:
     def join(self):
         if self.used:
             self.cur.wait_stream(self.side)
+
+
+_deferred = {"gen": 0, "forks": {}, "keep": []}
+
+
+def _defer_to_side(device, launch) -> None:
+    """Runs ``launch()`` on the side stream, ordered after everything queued on the current stream, WITHOUT joining:
+    the side stream runs in order, so the next ``_ParamGradFork.join()`` on this device covers it, and a callback at the
+    end of the backward pass joins whatever is still open (the optimizer and a graph capture see one stream again).
+    ``launch`` is kept alive until that join: it owns the scratch its kernel reads."""
+    fork = _ParamGradFork(device)
+    with fork:
+        launch()
+    _deferred["forks"][device.index] = fork
+    _deferred["keep"].append(launch)
+    gen = _deferred["gen"]
+    torch.autograd.Variable._execution_engine.queue_callback(lambda: _join_deferred(gen))
+
+
+def _join_deferred(gen: int) -> None:
+    if gen != _deferred["gen"]:
+        return                       # an earlier callback of this backward pass has joined already
+    _deferred["gen"] += 1
+    for fork in _deferred["forks"].values():
+        fork.join()
+    _deferred["forks"].clear()
+    _deferred["keep"].clear()
+
+
+def param_side_stream(device) -> Optional["torch.cuda.Stream"]:
+    """The side stream parameter-gradient kernels of ``device`` may be running on (None if none was made yet): a
+    consumer of gradients that runs before the end of the backward pass orders itself after it."""
+    return _side_streams.get(device.index if device.index is not None else torch.cuda.current_device())
 
 
 def _bias_grad_fork(dy2, b, needs: bool, fork: Optional[_ParamGradFork]):
@@ -282,6 +319,13 @@ class LayerNormFn(torch.autograd.Function):
             dres = dres.contiguous()
         tg, tb = _direct_grad(gamma), _direct_grad(beta)
         if tg is not None and (beta is None or tb is not None):
+            if _GRAD_SIDE and _NORM_DEFER and tb is not None:
+                # dx is what the backward pass waits for; the reduction of the parameter-gradient partials goes to
+                # the side stream, beside the GEMMs of the autograd node that follows
+                dx, _, _, finish = K.layernorm_bwd(xc, dy, gamma, mean, rstd, dres=dres, dgamma=tg, dbeta=tb,
+                                                   accumulate=True, defer_reduce=True)
+                _defer_to_side(dy.device, finish)
+                return dx, None, None, None, None
             dx, _, _ = K.layernorm_bwd(xc, dy, gamma, mean, rstd, dres=dres, dgamma=tg, dbeta=tb, accumulate=True)
             return dx, None, None, None, None
         dx, dg, db = K.layernorm_bwd(xc, dy, gamma, mean, rstd, dres=dres)

@@ -144,7 +144,10 @@ def layernorm_fwd(x, gamma, beta, eps):
     return y.view(x.shape), mean, rstd
 
 
-def layernorm_bwd(x, dy, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, accumulate=False):
+def layernorm_bwd(x, dy, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, accumulate=False, defer_reduce=False):
+    """``defer_reduce``: launch only the kernel that writes ``dx`` and the per-CTA partials of the parameter gradients,
+    and return a fourth value, a callable that launches their reduction into ``dgamma`` / ``dbeta`` on whatever stream
+    is current when it is called (it keeps the partials alive; the caller orders that stream after this call)."""
     lib = N.load()
     D = x.shape[-1]
     x2, dy2 = x.reshape(-1, D), dy.reshape(-1, D)
@@ -157,11 +160,20 @@ def layernorm_bwd(x, dy, gamma, mean, rstd, dres=None, dgamma=None, dbeta=None, 
         dbeta = torch.empty_like(gamma)
     prow = norm_partial_rows()
     partial = torch.empty(prow * 2 * D, dtype=torch.float32, device=x.device)
+    nparts = ctypes.c_int(0)
     N.check(lib.dptb_layernorm_bwd(x2.data_ptr(), dy2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
                                    N.ptr(None if dres is None else dres.reshape(-1, D)), dx.data_ptr(),
                                    dgamma.data_ptr(), dbeta.data_ptr(), partial.data_ptr(), prow, int(accumulate), rows,
-                                   D, N.dtype_code(x2), N.stream_ptr()), "layernorm_bwd")
-    return dx.view(x.shape), dgamma, dbeta
+                                   D, N.dtype_code(x2), N.stream_ptr(), int(defer_reduce), ctypes.byref(nparts)),
+            "layernorm_bwd")
+    if not defer_reduce:
+        return dx.view(x.shape), dgamma, dbeta
+    code = N.dtype_code(x2)
+
+    def finish():
+        N.check(lib.dptb_norm_param_grad_reduce(partial.data_ptr(), nparts.value, D, dgamma.data_ptr(), dbeta.data_ptr(),
+                                                int(accumulate), code, N.stream_ptr()), "norm_param_grad_reduce")
+    return dx.view(x.shape), dgamma, dbeta, finish
 
 
 def rmsnorm_fwd(x, gamma, eps, out=None):
@@ -191,7 +203,8 @@ def rmsnorm_bwd(x, dy, gamma, rstd, dres=None, dgamma=None, accumulate=False):
     partial = torch.empty(prow * 2 * D, dtype=torch.float32, device=x.device)
     N.check(lib.dptb_rmsnorm_bwd(x2.data_ptr(), dy2.data_ptr(), gamma.data_ptr(), rstd.data_ptr(),
                                  N.ptr(None if dres is None else dres.reshape(-1, D)), dx.data_ptr(), dgamma.data_ptr(),
-                                 partial.data_ptr(), prow, int(accumulate), rows, D, N.dtype_code(x2), N.stream_ptr()),
+                                 partial.data_ptr(), prow, int(accumulate), rows, D, N.dtype_code(x2), N.stream_ptr(),
+                                 0, None),
             "rmsnorm_bwd")
     return dx.view(x.shape), dgamma
 

@@ -93,7 +93,11 @@ class GradReducer:
         self._ready.clear()
 
     def _launch(self, b: int, exposed: bool = False) -> None:
+        from ..ops import cuda as _cu
         self._side.wait_stream(torch.cuda.current_stream())
+        extra = _cu.param_side_stream(self.arena.grad.device)   # bias sums / norm parameter gradients may run there
+        if extra is not None:
+            self._side.wait_stream(extra)
         with torch.cuda.stream(self._side):
             self.impl.reduce_bucket(b, exposed=exposed)
         self._launched.add(b)
