@@ -91,6 +91,53 @@ def test_training_step_on_arena_reduces_loss_and_checkpoint_round_trips():
     assert dp.Checkpoint.save_bytes(other)[:12] == blob[:12]
 
 
+def test_side_stream_parameter_gradients_equal_the_in_line_ones():
+    """Bias-gradient column sums and the norm layers' parameter-gradient reductions run on a side stream (joined
+    inside the backward pass): the arena must hold bit-identical gradients with that turned off, right after
+    ``backward()`` returns on the launching stream, also when the step is replayed from a CUDA graph."""
+    from dart_pytorch_b200.ops import cuda as C
+    _, gpu = _pair()
+    opt = dp.Adam(gpu.parameters(), lr=1e-3, weight_decay=0.1)
+    assert opt.arena is not None
+    g = torch.Generator().manual_seed(4)
+    x = torch.randint(0, 320, (4, 256), generator=g).cuda()
+    y = torch.roll(x, -1, 1)
+
+    def grads():
+        opt.zero_grad()
+        gpu.loss(x, y).backward()
+        return opt.arena.grad.clone()          # same stream as backward(): no synchronisation in between
+
+    saved = (C._GRAD_SIDE, C._NORM_DEFER)
+    try:
+        C._GRAD_SIDE, C._NORM_DEFER = False, False
+        ref = grads()
+        C._GRAD_SIDE, C._NORM_DEFER = True, False
+        only_bias = grads()
+        C._GRAD_SIDE, C._NORM_DEFER = True, True
+        both = grads()
+        assert torch.equal(only_bias, ref)
+        assert torch.equal(both, ref)
+        assert float(ref.float().abs().sum()) > 0
+        # captured: the fork / join events and the end-of-backward callback become part of the graph
+        static = torch.zeros_like(ref)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            grads()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                opt.zero_grad()
+                gpu.loss(x, y).backward()
+                static.copy_(opt.arena.grad)
+        torch.cuda.current_stream().wait_stream(s)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static, ref)
+    finally:
+        C._GRAD_SIDE, C._NORM_DEFER = saved
+
+
 def test_llama_loss_and_grads_match_cpu_reference():
     """Training path of the Llama family on the GPU: RMSNorm, in-place rotary embedding of the fused QKV output,
     grouped-query flash attention, SwiGLU, against the fp32 CPU reference of the same model."""
