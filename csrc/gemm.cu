@@ -1694,7 +1694,9 @@ static int gemm_impl(const DptbGemmArgs* a, const DptbTpArArgs* ar, const DptbTp
         const long long units = (long long)sched_tiles * sp;
         const double waves = (double)((units + sms - 1) / sms);
         const double per_kb = cand_bn == 256 ? 1.0 : 0.75;
-        const double fixed = (cand_bn == 256 ? 8.0 : 5.0) + (sp > 1 ? (cand_bn == 256 ? 6.0 + 1.5 * sp : 4.0 + 1.0 * sp) : 0.0);
+        // (the fold of a 256-wide tile is serial in its last CTA: measured on 768 x 768 x 16384, 8 splits of 256-wide tiles
+        // took 48 us against 42 us for 4 splits of 128-wide ones)
+        const double fixed = (cand_bn == 256 ? 8.0 : 5.0) + (sp > 1 ? (cand_bn == 256 ? 8.0 + 2.5 * sp : 4.0 + 1.0 * sp) : 0.0);
         const double cost = waves * (kbs * per_kb + fixed);
         if (cost < best) { best = cost; best_bn = cand_bn; best_sp = sp; }
       }
