@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -42,11 +43,21 @@ def kernel_head_dim(hd: int, backward: bool = False) -> Optional[int]:
     give zero output columns), sizes between 64 and 128 padded to 128 in forward.  ``None`` = no kernel for it."""
     if hd <= 0 or hd % 8:
         return None
+    if backward and deterministic():
+        return None          # the backward kernel sums dQ with fp32 atomics: run-to-run order is not fixed
     if hd <= 64:
         return 64
     if hd <= 128 and not backward:
         return 128
     return None
+
+
+def deterministic() -> bool:
+    """``DPTB200_DETERMINISTIC=1``: bit-identical results from run to run.  Every reduction in this package is ordered
+    (two-stage column sums, split-K folded in split order, sorted embedding scatter, fixed rank order in the collective
+    kernels) except the flash attention backward, whose dQ tiles from different key tiles meet in fp32 ``red.add``; with
+    the flag, attention that needs gradients takes the composed GEMM + softmax path instead."""
+    return os.environ.get("DPTB200_DETERMINISTIC", "0") not in ("0", "", "false", "False")
 
 
 def supported_head_dim(hd: int, backward: bool = False) -> bool:

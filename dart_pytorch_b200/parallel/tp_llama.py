@@ -34,6 +34,7 @@ from ..models.llama import Llama, LlamaConfig
 from ..ops import decode as D
 from ..ops import flash
 from ..ops import kernels as K
+from ..utils import trace
 from .tp import MAX_RANKS, TpComm, shard_range
 
 c_void_p, c_int, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
@@ -273,7 +274,8 @@ class TPLlamaEngine:
                 views.append((L.k_cache, L.v_cache))
                 L.k_cache, L.v_cache = L.k_cache[b0:b1], L.v_cache[b0:b1]
             try:
-                xo = self._blocks_sp(x, nb, S) if sp else self._blocks(x, nb, S, 0, device_pos=False)
+                with trace.range("tp/prefill_chunk"):
+                    xo = self._blocks_sp(x, nb, S) if sp else self._blocks(x, nb, S, 0, device_pos=False)
             finally:
                 for L, (kc, vc) in zip(self.layers, views):
                     L.k_cache, L.v_cache = kc, vc
@@ -294,10 +296,11 @@ class TPLlamaEngine:
         lib = N.load()
         lib.dptb_gemm_skinny_set_pdl(1 if pdl else 0)
         try:
-            x = self.comm.buffer(0, B)
-            x.copy_(K.embedding_fwd(self.embed, self.tokens[:B]))
-            xo = self._blocks(x, B, 1, 0, device_pos=True)
-            self._head(xo, B, advance=1)
+            with trace.range("tp/decode_step"):
+                x = self.comm.buffer(0, B)
+                x.copy_(K.embedding_fwd(self.embed, self.tokens[:B]))
+                xo = self._blocks(x, B, 1, 0, device_pos=True)
+                self._head(xo, B, advance=1)
         finally:
             lib.dptb_gemm_skinny_set_pdl(0)
 

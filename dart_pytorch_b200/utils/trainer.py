@@ -13,6 +13,7 @@ from typing import Callable, Optional
 import torch
 
 from ..optim.grad_utils import clip_grad_norm
+from . import trace
 
 
 class Trainer:
@@ -45,26 +46,32 @@ class Trainer:
 
     # ---- one eager step (also what gets captured) -------------------------------------------------
     def _device_step(self, x, y, split_optimizer: bool):
-        self.opt.zero_grad()
-        loss = self.loss_fn(self.model, x, y)
+        # Phases are named ranges (utils/trace.py): NVTX when enabled, device-timed under a PhaseTimer, else free.
+        with trace.range("step/forward"):
+            self.opt.zero_grad()
+            loss = self.loss_fn(self.model, x, y)
         if self.reducer is not None and hasattr(self.reducer, "begin_step"):
             self.reducer.begin_step()          # buckets may be reduced under the rest of the backward pass
-        loss.backward()
+        with trace.range("step/backward"):
+            loss.backward()
         norm = None
         clipped = False
         if self.reducer is not None:
-            has_ctrl = self.clip_norm is not None and getattr(self.opt, "arena", None) is not None
-            clipped = self.reducer.reduce(self.opt.ctrl if has_ctrl else None, self.clip_norm or 0.0)
+            with trace.range("step/grad_reduce"):
+                has_ctrl = self.clip_norm is not None and getattr(self.opt, "arena", None) is not None
+                clipped = self.reducer.reduce(self.opt.ctrl if has_ctrl else None, self.clip_norm or 0.0)
             if clipped:
                 from ..optim.grad_utils import LazyScalar
                 self.opt.clip_pending = True
                 norm = LazyScalar(self.opt.ctrl, 0)
         if self.clip_norm is not None and not clipped:
-            norm = clip_grad_norm(self.opt, self.clip_norm)
-        if split_optimizer:
-            self.opt.launch_step()
-        else:
-            self.opt.step()
+            with trace.range("step/clip"):
+                norm = clip_grad_norm(self.opt, self.clip_norm)
+        with trace.range("step/optimizer"):
+            if split_optimizer:
+                self.opt.launch_step()
+            else:
+                self.opt.step()
         return loss, norm
 
     def _capture(self, x, y):

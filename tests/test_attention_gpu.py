@@ -135,6 +135,34 @@ def test_self_attention_module_gradients(hd, heads, kv_heads):
         assert pd.grad is not None and _rel(pd.grad.cpu(), pr.grad) < 5e-2
 
 
+def test_deterministic_option_gives_bit_identical_attention_gradients(monkeypatch):
+    """``DPTB200_DETERMINISTIC=1`` takes attention that needs gradients off the flash backward kernel (whose dQ tiles
+    meet in fp32 atomics): two runs are then bit-identical, and still match the fp32 module."""
+    from dart_pytorch_b200.nn.attention import MultiHeadAttention
+    monkeypatch.setenv("DPTB200_DETERMINISTIC", "1")
+    assert A.kernel_head_dim(64, backward=True) is None and A.kernel_head_dim(64) == 64
+    D, heads = 256, 4
+    ref = MultiHeadAttention(D, heads, bias=True, seed=3)
+    dev = MultiHeadAttention(D, heads, bias=True, seed=3).to("cuda", torch.bfloat16)
+    torch.manual_seed(1)
+    x = torch.randn(2, 384, D)
+    g = torch.randn(2, 384, D)
+    runs = []
+    for _ in range(2):
+        xd = x.to("cuda", torch.bfloat16).requires_grad_(True)
+        for p in dev.parameters():
+            p.grad = None
+        before = _launches()
+        dev(xd, causal=True).backward(g.to("cuda", torch.bfloat16))
+        runs.append([xd.grad.clone()] + [p.grad.clone() for p in dev.parameters()])
+        assert _launches() > before
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+    xr = x.clone().requires_grad_(True)
+    ref(xr, causal=True).backward(g)
+    assert _rel(runs[0][0].cpu(), xr.grad) < 5e-2
+
+
 @pytest.mark.parametrize("hd", [32, 128, 64])
 def test_cross_attention_module_gradients(hd):
     from dart_pytorch_b200.nn.attention import MultiHeadCrossAttention
