@@ -71,7 +71,8 @@ embedding_bwd_atomic_kernel(T* __restrict__ dtable, long long vocab, const long 
 template <typename T>
 __global__ void __launch_bounds__(256)
 embedding_bwd_sorted_kernel(T* __restrict__ dtable, long long vocab, const long long* __restrict__ sorted_idx,
-                            const long long* __restrict__ perm, const T* __restrict__ dout, long long n, int D) {
+                            const long long* __restrict__ perm, const T* __restrict__ dout, long long n, int D,
+                            int vec_ok) {
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
@@ -81,10 +82,25 @@ embedding_bwd_sorted_kernel(T* __restrict__ dtable, long long vocab, const long 
     if (i > 0 && sorted_idx[i - 1] == t) continue;  // not a run start
     long long end = i + 1;
     while (end < n && sorted_idx[end] == t) ++end;
-    for (int c = lane; c < D; c += 32) {
-      float acc = to_f32(dtable[t * D + c]);
-      for (long long k = i; k < end; ++k) acc += to_f32(dout[perm[k] * D + c]);
-      dtable[t * D + c] = from_f32<T>(acc);
+    if (vec_ok) {
+      // 16-byte accesses: a lane owns 8 consecutive features of the row, rows of the run are added in order
+      for (int c = lane * 8; c < D; c += 256) {
+        float acc[8];
+        Vec8<T>::load(dtable + t * D + c, acc);
+        for (long long k = i; k < end; ++k) {
+          float v[8];
+          Vec8<T>::load(dout + perm[k] * D + c, v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += v[j];
+        }
+        Vec8<T>::store(dtable + t * D + c, acc);
+      }
+    } else {
+      for (int c = lane; c < D; c += 32) {
+        float acc = to_f32(dtable[t * D + c]);
+        for (long long k = i; k < end; ++k) acc += to_f32(dout[perm[k] * D + c]);
+        dtable[t * D + c] = from_f32<T>(acc);
+      }
     }
   }
 }
@@ -134,8 +150,9 @@ extern "C" int dptb_embedding_bwd(void* dtable, long long vocab, const long long
   if (n <= 0) return 0;
   auto st = static_cast<cudaStream_t>(stream);
   if (sorted_idx && perm) {
-    if (dtype) embedding_bwd_sorted_kernel<__nv_bfloat16><<<warp_grid(n), 256, 0, st>>>((__nv_bfloat16*)dtable, vocab, sorted_idx, perm, (const __nv_bfloat16*)dout, n, D);
-    else       embedding_bwd_sorted_kernel<float><<<warp_grid(n), 256, 0, st>>>((float*)dtable, vocab, sorted_idx, perm, (const float*)dout, n, D);
+    const int vec_ok = (D % 8 == 0) && (((reinterpret_cast<uintptr_t>(dtable) | reinterpret_cast<uintptr_t>(dout)) & 15) == 0);
+    if (dtype) embedding_bwd_sorted_kernel<__nv_bfloat16><<<warp_grid(n), 256, 0, st>>>((__nv_bfloat16*)dtable, vocab, sorted_idx, perm, (const __nv_bfloat16*)dout, n, D, vec_ok);
+    else       embedding_bwd_sorted_kernel<float><<<warp_grid(n), 256, 0, st>>>((float*)dtable, vocab, sorted_idx, perm, (const float*)dout, n, D, vec_ok);
   } else {
     if (dtype) embedding_bwd_atomic_kernel<__nv_bfloat16><<<warp_grid(n), 256, 0, st>>>((__nv_bfloat16*)dtable, vocab, idx, (const __nv_bfloat16*)dout, n, D);
     else       embedding_bwd_atomic_kernel<float><<<warp_grid(n), 256, 0, st>>>((float*)dtable, vocab, idx, (const float*)dout, n, D);
