@@ -52,6 +52,12 @@ def test_tp_llama_engine_matches_whole_model(hd, world):
     _run("tp_llama_worker.py", hd, nproc=world, port=29545 + (hd == "128"), ok="tp_llama_worker ok")
 
 
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+def test_tp_llama_engine_single_rank():
+    """The engine as a one-GPU serving path (a group of one rank: no peers, no multicast): same parity check."""
+    _run("tp_llama_worker.py", "128", nproc=1, port=29549, ok="tp_llama_worker ok")
+
+
 @needs2
 @pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("cf", ["1.25", "0.5"])
