@@ -122,7 +122,7 @@ def dropout(x, p: float, training: bool, generator: Optional[torch.Generator] = 
     # whose cost is the generator's bernoulli path; autograd sees a plain multiply by the scaled mask.
     n = x.numel()
     words = torch.empty((n + 3) // 4, dtype=torch.int64, device=x.device).random_(-2 ** 63, None)
-    keep = words.view(torch.int16)[:n].view(x.shape) >= (-32768 + int(round(p * 65536.0)))
+    keep = words.view(torch.int16)[:n].view(x.shape) >= min(32767, -32768 + int(round(p * 65536.0)))
     return x * keep.to(x.dtype).mul_(1.0 / (1.0 - p))
 
 
