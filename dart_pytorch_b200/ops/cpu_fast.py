@@ -120,9 +120,11 @@ def dropout(x, p: float, training: bool, generator: Optional[torch.Generator] = 
     # generator (so ``torch.manual_seed`` governs it), viewed as int16 and compared with the threshold for ``p``
     # (resolution 2^-16).  Three times cheaper than ``torch.native_dropout`` on the tensors of a small CPU model,
     # whose cost is the generator's bernoulli path; autograd sees a plain multiply by the scaled mask.
+    if p < 2e-3 or p > 1.0 - 2e-3:
+        return torch.native_dropout(x, p, True)[0]      # beyond what 16 bits resolve: the generator's bernoulli path
     n = x.numel()
     words = torch.empty((n + 3) // 4, dtype=torch.int64, device=x.device).random_(-2 ** 63, None)
-    keep = words.view(torch.int16)[:n].view(x.shape) >= min(32767, -32768 + int(round(p * 65536.0)))
+    keep = words.view(torch.int16)[:n].view(x.shape) >= (-32768 + int(round(p * 65536.0)))
     return x * keep.to(x.dtype).mul_(1.0 / (1.0 - p))
 
 
